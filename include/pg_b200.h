@@ -399,6 +399,68 @@ int pg_moe_combine(float* x, const void* y, int ldy, const int32_t* pair_pos, co
                    int ldh, const void* shared_out, int lds, const float* shared_gate, int n_tokens, int D, int top,
                    int dtype, void* stream);
 
+/* pairings of the two products of a stacked [Wg; Wu] weight (pg_moe_gemm_act, pg_glu_clamped) */
+enum {
+  PG_GLU_NONE = 0,
+  PG_GLU_SILU = 1,    /* silu(g) * u */
+  PG_GLU_CLAMPED = 2  /* g' = min(g, limit), u' = clamp(u, -limit, limit): g' sigmoid(1.702 g') (u' + 1) */
+};
+
+/* pg_moe_gemm with the pairing given by name (pg_moe_gemm: swiglu != 0 is PG_GLU_SILU). */
+int pg_moe_gemm_act(void* out, int ldo, const void* A, int lda, const int32_t* row_map, const void* W,
+                    const int32_t* offsets, int n_pairs, int n_experts, int N, int K, int act, float limit, int impl,
+                    int* err_flag, int dtype, void* stream);
+/* Router with sigmoid scores and expert groups: z = h W_router^T in fp32, s = sigmoid(z), choice c = s + correction
+ * (correction may be NULL).  The n_route experts form n_groups equal groups of neighbours; a group's score is the sum
+ * of its two largest choice scores, only experts of the `keep` best groups can be chosen; the `top` largest choice
+ * scores are chosen (ties: lowest index) and topk_w = s[chosen] / (sum of the chosen s + 1e-20). */
+int pg_moe_route_grouped(int32_t* topk_idx, float* topk_w, const void* h, int ldh, const void* w_router,
+                         const void* correction, int n_tokens, int D, int n_route, int top, int n_groups, int keep,
+                         int dtype, void* stream);
+/* out[t] = sum_k topk_w[t,k] * y[pair_pos[t,k]] + shared_out[t] (shared_out may be NULL), rounded to the model dtype:
+ * the feed-forward output of designs that norm it before the residual sum. */
+int pg_moe_combine_out(void* out, int ldo, const void* y, int ldy, const int32_t* pair_pos, const float* topk_w,
+                       const void* shared_out, int lds, int n_tokens, int D, int top, int dtype, void* stream);
+/* out[r, c] = g sigmoid(alpha g) (u + 1), g = min(gate_up[r, c], limit), u = clamp(gate_up[r, F + c], -limit, limit). */
+int pg_glu_clamped(void* out, const void* gate_up, int rows, int F, float limit, float alpha, int dtype, void* stream);
+
+/* ---- lightning attention: linear attention with a constant decay per head ------------------------------------------
+ * Per head, state S [dim x vdim] in fp32 per sequence slot ([slots][heads][dim][vdim]); q, k, v = silu of the fused
+ * projection's columns at q_col0 / k_col0 / v_col0 (heads x dim, heads x dim, heads x vdim):
+ *   S <- decay[h] S + k v^T;  o = S^T q.   segs as for pg_delta_rule; out fp32 [n_tokens, heads * vdim]. */
+int pg_lightning_attention(float* out, float* state, const void* proj, int ld, int q_col0, int k_col0, int v_col0,
+                           const float* decay, const int32_t* segs, int n_segs, int heads, int dim, int vdim, int dtype,
+                           void* stream);
+
+/* ---- latent attention ------------------------------------------------------------------------------------------
+ * pg_latent_prep: from the fused projection row [.. dq (q_rank) .. dkv (kv_rank + rot_dim) ..]:
+ *   cq_out[t] = RMS(dq) * w_q (model dtype, packed [n_tokens, q_rank]);
+ *   pool row of (tok_slot, tok_pos) = [RMS(dkv[:kv_rank]) * w_kv | rotary(dkv[kv_rank:]) | zeros up to ld_pool]
+ *   (pairs (2i, 2i+1), angle pos * freq[i], cos and sin times mag, fp32).
+ * pg_rotary_cols: the same rotation of rot_dim columns of every head of a row into another matrix.
+ * pg_head_gemm: out[t, h*out_head_stride + n] = sum_k A[t, h*a_head_stride + k] W[h][n][k] for all heads (W is
+ *   [heads][N][K]), times sigmoid(gate[t, h*N + n]) when a gate is given; fp32 accumulation, one rounding.
+ * pg_attention_ragged_sink: pg_attention_ragged_ex with explicit row strides of the two pools (0: packed) and
+ *   sink (device fp32 [n_heads], may be NULL): exp(sink[h]) is added once to the softmax denominator.
+ * pg_concat_cast: out[r] = [a[r] | b[r]] of two fp32 [rows, D] matrices in the model dtype. */
+int pg_latent_prep(void* cq_out, const void* proj, int ld, int dq_col0, int q_rank, const void* w_q, int dkv_col0,
+                   int kv_rank, const void* w_kv, int rot_dim, const float* freq, float mag, float eps, void* pool,
+                   int ld_pool, const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,
+                   const int32_t* tok_pos, int n_tokens, int dtype, void* stream);
+int pg_rotary_cols(void* dst, int ld_dst, int dst_col0, int dst_head_stride, const void* src, int ld_src, int src_col0,
+                   int src_head_stride, int heads, int rot_dim, const float* freq, float mag, const int32_t* tok_pos,
+                   int n_tokens, int dtype, void* stream);
+int pg_head_gemm(void* out, int ldo, int out_head_stride, const void* A, int lda, int a_head_stride, const void* W,
+                 const void* gate, int ld_gate, int n_rows, int heads, int N, int K, int dtype, void* stream);
+int pg_attention_ragged_sink(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                             int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
+                             const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,
+                             const int32_t* tok_pos, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
+                             float scale, int window, int keep_first, const float* slopes, int sigmoid_weights,
+                             const float* head_bias, const float* sink, float out_scale, float* ws, long long ws_floats,
+                             int dtype, void* stream);
+int pg_concat_cast(void* out, const float* a, const float* b, int rows, int D, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,6 +12,9 @@
 // [0, min(keep_first, lo)) ++ [lo, p], which every kernel below walks through one index map.  weights == 1 replaces
 // the softmax by unnormalised weights sigmoid(score + head_bias[h]).  The gate is either one value per output column
 // (gate_per_head == 0) or one per (token, head); the result is multiplied by out_scale before the single rounding.
+// pg_attention_ragged_sink adds: sink[h], a per-head logit without key or value whose exp joins the softmax
+// denominator once (after all partial sums are merged), and explicit row strides of the key and the value pool, so
+// that the value rows may be a prefix of the key rows of ONE pool (latent attention: key [c | k_rot], value c).
 //
 // attention_ragged_kernel: one warp per (token, head).  32 keys per iteration, one key per lane for the dot
 // product (the query row lives in shared memory as fp32), running (max, sum) rescaling, then the lanes switch to the
@@ -96,6 +99,8 @@ struct RagAttnParams {
   const float* head_bias;        // per query head, added to the score (NULL: none)
   int gate_per_head;             // 0: gate[t][h * vdim + c]; 1: gate[t][h]
   float out_scale;
+  int ld_k, ld_v;                // elements between the rows of the key / value pool (>= G * dim, G * vdim)
+  const float* sink;             // per query head: exp(sink[h]) joins the softmax denominator (no key, no value)
 };
 
 // The visible keys of a token at position pos as one list: n_keep kept first positions, then [lo, pos].
@@ -118,7 +123,7 @@ __device__ __forceinline__ void attend_range(const RagAttnParams& p, const float
   const int lane = threadIdx.x & 31;
   const T* kpool = reinterpret_cast<const T*>(p.k_pool);
   const T* vpool = reinterpret_cast<const T*>(p.v_pool);
-  const int kw = p.G * p.dim, vw = p.G * p.vdim;
+  const int kw = p.ld_k, vw = p.ld_v;
   for (int j0 = lo; j0 <= hi; j0 += 32) {
     const bool valid = j0 + lane <= hi;
     const int j = kr.key(j0 + lane);
@@ -141,7 +146,7 @@ __device__ __forceinline__ void attend_range(const RagAttnParams& p, const float
       for (int i = 0; i < DPL; ++i) acc[i] *= corr;
     }
     const int n = min(32, hi - j0 + 1);
-    const bool vecv = p.vdim == 32 * DPL && DPL * sizeof(T) >= 4 && DPL * sizeof(T) <= 16;   // lane = DPL contiguous columns
+    const bool vecv = p.vdim == 32 * DPL && DPL * sizeof(T) >= 4 && DPL * sizeof(T) <= 16 && vw % DPL == 0;   // lane = DPL contiguous columns
 #pragma unroll 8
     for (int jj = 0; jj < n; ++jj) {
       const float w = __shfl_sync(0xffffffffu, pj, jj);
@@ -163,8 +168,9 @@ __device__ __forceinline__ void attend_range(const RagAttnParams& p, const float
 }
 
 template <typename T, int DPL>
-__device__ __forceinline__ void store_out(const RagAttnParams& p, int t, int h, float l, const float* acc) {
+__device__ __forceinline__ void store_out(const RagAttnParams& p, int t, int h, float m, float l, const float* acc) {
   const int lane = threadIdx.x & 31;
+  if (p.sink && !p.sigmoid_weights) l += expf(p.sink[h] - m);      // m: the maximum the sums are relative to
   T* o = reinterpret_cast<T*>(p.out) + (size_t)t * p.ld_out + h * p.vdim;
   const T* gt = (p.gate && !p.gate_per_head) ? reinterpret_cast<const T*>(p.gate) + (size_t)t * p.ld_gate + h * p.vdim : nullptr;
   float inv = (p.sigmoid_weights ? 1.f : 1.f / l) * p.out_scale;
@@ -202,7 +208,7 @@ __global__ void __launch_bounds__(256) attention_ragged_kernel(RagAttnParams p) 
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
   attend_range<T, DPL>(p, qs, pt_row, g, pos, slope, bias, kr, m, l, acc);
-  store_out<T, DPL>(p, t, h, l, acc);
+  store_out<T, DPL>(p, t, h, m, l, acc);
 }
 
 // R query rows against one key row: one pass over the key, R independent accumulators.
@@ -258,8 +264,8 @@ __global__ void __launch_bounds__(128) attention_ragged_split_kernel(RagAttnPara
   }
   const T* kpool = reinterpret_cast<const T*>(p.k_pool);
   const T* vpool = reinterpret_cast<const T*>(p.v_pool);
-  const int kw = p.G * p.dim, vw = p.G * p.vdim;
-  const bool vecv = p.vdim == 32 * DPL && DPL * sizeof(T) >= 4 && DPL * sizeof(T) <= 16;
+  const int kw = p.ld_k, vw = p.ld_v;
+  const bool vecv = p.vdim == 32 * DPL && DPL * sizeof(T) >= 4 && DPL * sizeof(T) <= 16 && vw % DPL == 0;
   // this CTA's slice of the visible keys: whole 32-key blocks
   const int blocks = (kr.count + 31) / 32, per = (blocks + gridDim.y - 1) / gridDim.y;
   const int b_begin = blockIdx.y * per, b_end = min(blocks, b_begin + per);
@@ -342,7 +348,7 @@ __global__ void __launch_bounds__(128) attention_ragged_split_kernel(RagAttnPara
 #pragma unroll
       for (int i = 0; i < DPL; ++i) a[i] += pw[2 + lane * DPL + i] * c;
     }
-    if (gridDim.y == 1) { store_out<T, DPL>(p, t, h0 + r, Lsum, a); continue; }
+    if (gridDim.y == 1) { store_out<T, DPL>(p, t, h0 + r, M, Lsum, a); continue; }
     float* o = ws + (((size_t)t * p.H + h0 + r) * gridDim.y + blockIdx.y) * PW;
     if (lane == 0) { o[0] = M; o[1] = Lsum; }
 #pragma unroll
@@ -371,7 +377,7 @@ __global__ void attention_ragged_merge_kernel(RagAttnParams p, const float* __re
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] += pw[2 + lane * DPL + i] * c;
   }
-  store_out<T, DPL>(p, item / p.H, item % p.H, Lsum, acc);
+  store_out<T, DPL>(p, item / p.H, item % p.H, M, Lsum, acc);
 }
 
 template <typename T, int DPL, int R>
@@ -391,7 +397,7 @@ static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats,
   const long long items = (long long)p.n_tokens * p.H;
   static const int split_max = env_int("PG_RAGGED_SPLIT_MAX_ITEMS", 592);   // below 4 (token, head) pairs per SM
   const int R = p.H / p.G;
-  const bool r_ok = R == 1 || R == 2 || R == 4 || (R == 8 && DPL <= 4);
+  const bool r_ok = R == 1 || R == 2 || (R == 4 && DPL <= 8) || (R == 8 && DPL <= 4);
   if (items <= split_max && r_ok && (p.window <= 0 || p.window > 64)) {
     // key slices until about two CTAs per SM are busy; a slice holds at least 128 keys (one block per warp)
     const long long ctas = (long long)p.n_tokens * p.G;
@@ -403,7 +409,7 @@ static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats,
     switch (R) {
       case 1: return launch_split<T, DPL, 1>(p, ws, slices, st);
       case 2: return launch_split<T, DPL, 2>(p, ws, slices, st);
-      case 4: return launch_split<T, DPL, 4>(p, ws, slices, st);
+      case 4: return launch_split<T, (DPL <= 8 ? DPL : 8), 4>(p, ws, slices, st);
       default: return launch_split<T, (DPL <= 4 ? DPL : 4), 8>(p, ws, slices, st);
     }
   }
@@ -417,6 +423,36 @@ static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats,
 
 using namespace pg;
 
+extern "C" int pg_attention_ragged_sink(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                        int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
+                                        const int32_t* page_table, int pt_stride, int page_size,
+                                        const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens, int n_heads,
+                                        int n_kv_heads, int dim, int vdim, float scale, int window, int keep_first,
+                                        const float* slopes, int sigmoid_weights, const float* head_bias,
+                                        const float* sink, float out_scale, float* ws, long long ws_floats, int dtype,
+                                        void* stream) {
+  if (n_tokens <= 0) return PG_OK;
+  if (ld_k <= 0) ld_k = n_kv_heads * dim;
+  if (ld_v <= 0) ld_v = n_kv_heads * vdim;
+  PG_REQUIRE(ld_k >= n_kv_heads * dim && ld_v >= n_kv_heads * vdim, "attention_ragged: pool rows of %d / %d elements", ld_k, ld_v);
+  PG_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_ragged: heads %d / kv heads %d",
+             n_heads, n_kv_heads);
+  PG_REQUIRE(dim > 0 && dim <= 1024 && vdim > 0 && vdim <= 512, "attention_ragged: dim %d (<= 1024), vdim %d (<= 512)", dim, vdim);
+  RagAttnParams p = {out, ld_out, q, ld_q, gate, ld_gate, k_pool, v_pool, page_table, pt_stride, page_size, tok_slot,
+                     tok_pos, n_tokens, n_heads, n_kv_heads, dim, vdim, scale, window, slopes, keep_first,
+                     sigmoid_weights ? 1 : 0, head_bias, gate_per_head ? 1 : 0, out_scale, ld_k, ld_v, sink};
+  cudaStream_t st = (cudaStream_t)stream;
+  const int dpl = (vdim + 31) / 32;
+  PG_DISPATCH_DTYPE(dtype, T, {
+    if (dpl <= 1) return launch_ragged<T, 1>(p, ws, ws_floats, st);
+    if (dpl <= 2) return launch_ragged<T, 2>(p, ws, ws_floats, st);
+    if (dpl <= 4) return launch_ragged<T, 4>(p, ws, ws_floats, st);
+    if (dpl <= 8) return launch_ragged<T, 8>(p, ws, ws_floats, st);
+    return launch_ragged<T, 16>(p, ws, ws_floats, st);
+  });
+  return PG_OK;
+}
+
 extern "C" int pg_attention_ragged_ex(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
                                       int gate_per_head, const void* k_pool, const void* v_pool,
                                       const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,
@@ -424,22 +460,10 @@ extern "C" int pg_attention_ragged_ex(void* out, int ld_out, const void* q, int 
                                       int vdim, float scale, int window, int keep_first, const float* slopes,
                                       int sigmoid_weights, const float* head_bias, float out_scale, float* ws,
                                       long long ws_floats, int dtype, void* stream) {
-  if (n_tokens <= 0) return PG_OK;
-  PG_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_ragged: heads %d / kv heads %d",
-             n_heads, n_kv_heads);
-  PG_REQUIRE(dim > 0 && dim <= 512 && vdim > 0 && vdim <= 256, "attention_ragged: dim %d (<= 512), vdim %d (<= 256)", dim, vdim);
-  RagAttnParams p = {out, ld_out, q, ld_q, gate, ld_gate, k_pool, v_pool, page_table, pt_stride, page_size, tok_slot,
-                     tok_pos, n_tokens, n_heads, n_kv_heads, dim, vdim, scale, window, slopes, keep_first,
-                     sigmoid_weights ? 1 : 0, head_bias, gate_per_head ? 1 : 0, out_scale};
-  cudaStream_t st = (cudaStream_t)stream;
-  const int dpl = (vdim + 31) / 32;
-  PG_DISPATCH_DTYPE(dtype, T, {
-    if (dpl <= 1) return launch_ragged<T, 1>(p, ws, ws_floats, st);
-    if (dpl <= 2) return launch_ragged<T, 2>(p, ws, ws_floats, st);
-    if (dpl <= 4) return launch_ragged<T, 4>(p, ws, ws_floats, st);
-    return launch_ragged<T, 8>(p, ws, ws_floats, st);
-  });
-  return PG_OK;
+  return pg_attention_ragged_sink(out, ld_out, q, ld_q, gate, ld_gate, gate_per_head, k_pool, 0, v_pool, 0, page_table,
+                                  pt_stride, page_size, tok_slot, tok_pos, n_tokens, n_heads, n_kv_heads, dim, vdim, scale,
+                                  window, keep_first, slopes, sigmoid_weights, head_bias, nullptr, out_scale, ws, ws_floats,
+                                  dtype, stream);
 }
 
 extern "C" int pg_attention_ragged(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,

@@ -24,6 +24,8 @@ struct MoeParams {
   const int32_t* offsets;
   int n_experts, N, K, ldo;
   int* err_flag;   // device-visible int, set to 2 when a pipeline wait gave up (may be NULL)
+  int act;         // pairing of the two products of a stacked [Wg; Wu] tile: PG_GLU_SILU or PG_GLU_CLAMPED
+  float limit;     // PG_GLU_CLAMPED: g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1)
 };
 
 // Every wait of this kernel is bounded: if the roles ever disagreed about the tile sequence (the offsets are data),
@@ -190,7 +192,16 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               float x = rnd<T>(v[j0 + j]);
-              if (DUAL) x = rnd<T>(rnd<T>(x / (1.f + __expf(-x))) * rnd<T>(u[DUAL ? j0 + j : 0]));
+              if (DUAL) {
+                float uu = rnd<T>(u[DUAL ? j0 + j : 0]);
+                if (p.act == PG_GLU_CLAMPED) {
+                  x = fminf(x, p.limit);
+                  uu = fminf(fmaxf(uu, -p.limit), p.limit);
+                  x = rnd<T>(x / (1.f + __expf(-1.702f * x))) * (uu + 1.f);
+                } else {
+                  x = rnd<T>(rnd<T>(x / (1.f + __expf(-x))) * uu);
+                }
+              }
               o[j] = x;
             }
             *reinterpret_cast<uint4*>(out + (size_t)m * p.ldo + n0 + j0) = pack<T>(o);
@@ -241,8 +252,9 @@ bool moe_gemm_tc_supported(int ldo, int lda, const int32_t* row_map, int N, int 
 }
 
 int moe_gemm_tc(void* out, int ldo, const void* A, int lda, const int32_t* row_map, const void* W,
-                const int32_t* offsets, int n_pairs, int n_experts, int N, int K, int swiglu, int dtype,
+                const int32_t* offsets, int n_pairs, int n_experts, int N, int K, int act, float limit, int dtype,
                 int* err_flag, cudaStream_t st) {
+  const int swiglu = act != PG_GLU_NONE;
   (void)row_map;
   PG_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)out % 16) == 0,
              "moe_gemm_tc: operands must be 16-byte aligned");
@@ -253,7 +265,7 @@ int moe_gemm_tc(void* out, int ldo, const void* A, int lda, const int32_t* row_m
   PG_REQUIRE(tc::make_map_2d(&ma, A, n_pairs, K, lda, tc::MG_BM, bf) &&
                  tc::make_map_2d(&mw, W, (long long)n_experts * rows_per_expert, K, K, bn, bf),
              "moe_gemm_tc: cuTensorMapEncodeTiled failed (rows=%d N=%d K=%d)", n_pairs, N, K);
-  tc::MoeParams p = {out, offsets, n_experts, N, K, ldo, err_flag};
+  tc::MoeParams p = {out, offsets, n_experts, N, K, ldo, err_flag, act, limit};
   const int max_tiles = (cdiv(n_pairs, tc::MG_BM) + n_experts) * cdiv(N, bn);
 #define PG_MOE(D, B) return bf ? tc::launch_moe<bf16, D, B>(ma, mw, p, max_tiles, st) : tc::launch_moe<f16, D, B>(ma, mw, p, max_tiles, st)
   if (swiglu) { if (bn == 128) { PG_MOE(true, 128); } PG_MOE(true, 64); }

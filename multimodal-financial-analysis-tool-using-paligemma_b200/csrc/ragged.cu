@@ -140,6 +140,20 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
   }
 }
 
+// The clamped pairing of a stacked [gate | up] row: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g sigmoid(alpha g) (u + 1); the activation is rounded to the model dtype before the product.
+template <typename T>
+__global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ gu, int rows, int F, float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)rows * F;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / F, c = i % F;
+    const float g = fminf(to_f<T>(gu[r * 2 * F + c]), limit);
+    const float u = fminf(fmaxf(to_f<T>(gu[r * 2 * F + F + c]), -limit), limit);
+    out[i] = from_f<T>(rnd<T>(g / (1.f + expf(-alpha * g))) * (u + 1.f));
+  }
+}
 
 // ------------------------------------------------------------------ bias + rotary positions + value mixing + cache append
 // One CTA per token.  proj row = [.. q (H heads x dim) .. k (G x dim) .. v (G x vdim) ..] at the given column offsets.
@@ -352,6 +366,18 @@ extern "C" int pg_swiglu(void* out, const void* gate_up, int rows, int F, int dt
   PG_DISPATCH_DTYPE(dtype, T, {
     return launch_pdl("swiglu", swiglu_kernel<T, false>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
                       (const T*)gate_up, rows, F);
+  });
+  return PG_OK;
+}
+
+extern "C" int pg_glu_clamped(void* out, const void* gate_up, int rows, int F, float limit, float alpha, int dtype,
+                              void* stream) {
+  if (rows <= 0 || F <= 0) return PG_OK;
+  const long long n = (long long)rows * F;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  PG_DISPATCH_DTYPE(dtype, T, {
+    return launch_pdl("glu_clamped", glu_clamped_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                      (const T*)gate_up, rows, F, limit, alpha);
   });
   return PG_OK;
 }

@@ -1,4 +1,5 @@
-// Recurrent mixers for ragged token batches: the generalised delta rule with a per-channel decay.
+// Recurrent mixers for ragged token batches: the generalised delta rule with a per-channel decay, and lightning
+// attention (linear attention with a constant decay per head; described at its kernel below).
 //
 // Per head, with a state S [dim x dim] (key channel i, value column j) kept in fp32 per sequence slot:
 //     u   = k / sqrt(sum(k^2) + key_eps)
@@ -260,6 +261,118 @@ __global__ void headnorm_gate_kernel(T* __restrict__ out, int ld_out, const floa
   }
 }
 
+// ------------------------------------------------------------------ lightning attention: linear attention with a constant decay per head
+// Per head, with a state S [dim x vdim] (key channel i, value column j) kept in fp32 per sequence slot:
+//     q = silu(q_pre), k = silu(k_pre), v = silu(v_pre)          (pre-activations: the fused projection, model dtype)
+//     S <- decay_h S + k v^T,        o = S^T q
+// One CTA per (sequence segment, head, slice of VT value columns).  A thread owns a quarter of the rows of one value
+// column (the layout of the delta-rule kernel above: rows 4 (m RG + rg) + e), so a token costs one fused multiply-add
+// per state element for the update, one for the output, and two shuffle steps.  The activated q and k of CH tokens and
+// the slice's v are staged in shared memory as fp32; the state is read from and written back to the slot once per
+// launch, which makes a prompt portion and a single decoded token the same case and the result independent of where
+// the sequence was cut.
+template <typename T, int DMAX, int CH>
+__global__ void __launch_bounds__(256)
+lightning_kernel(float* __restrict__ out, float* __restrict__ state, const T* __restrict__ proj, int ld, int q_col0,
+                 int k_col0, int v_col0, const float* __restrict__ decay, const int32_t* __restrict__ segs, int heads,
+                 int dim, int vdim) {
+  constexpr int RG = 4, NG = DMAX / (4 * RG);
+  extern __shared__ __align__(16) float sh[];       // q [CH][DMAX] | k [CH][DMAX] | v [CH][VT]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int32_t* sg = segs + 3 * (size_t)blockIdx.x;
+  const int slot = sg[0], row0 = sg[1], n = sg[2];
+  if (n <= 0) return;
+  const int VT = blockDim.x / RG;
+  float* qs = sh;
+  float* ks = sh + CH * DMAX;
+  float* vs = sh + 2 * CH * DMAX;
+  const int h = blockIdx.y, j0 = blockIdx.z * VT, jl = threadIdx.x / RG, j = j0 + jl, rg = threadIdx.x % RG;
+  const bool live = j < vdim;
+  const float lam = decay[h];
+  float S[NG * 4];
+  float* st = state + ((size_t)slot * heads + h) * dim * vdim;
+#pragma unroll
+  for (int m = 0; m < NG; ++m)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 4 * (m * RG + rg) + e;
+      S[m * 4 + e] = (live && i < dim) ? st[(size_t)i * vdim + j] : 0.f;
+    }
+  const int nv = min(VT, vdim - j0);
+  for (int t0 = 0; t0 < n; t0 += CH) {
+    const int nt = min(CH, n - t0);
+    for (int idx = threadIdx.x; idx < nt * DMAX; idx += blockDim.x) {
+      const int tt = idx / DMAX, c = idx % DMAX;
+      float a = 0.f, b = 0.f;
+      if (c < dim) {
+        const T* row = proj + (size_t)(row0 + t0 + tt) * ld + h * dim + c;
+        a = to_f<T>(row[q_col0]);
+        b = to_f<T>(row[k_col0]);
+        a = a * sigmoid_f(a);
+        b = b * sigmoid_f(b);
+      }
+      qs[idx] = a;
+      ks[idx] = b;
+    }
+    for (int idx = threadIdx.x; idx < nt * VT; idx += blockDim.x) {
+      const int tt = idx / VT, c = idx % VT;
+      float a = 0.f;
+      if (c < nv) {
+        a = to_f<T>(proj[(size_t)(row0 + t0 + tt) * ld + v_col0 + h * vdim + j0 + c]);
+        a = a * sigmoid_f(a);
+      }
+      vs[idx] = a;
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int tt = 0; tt < nt; ++tt) {
+      const float vj = vs[tt * VT + jl];
+      const float* qr = qs + tt * DMAX + 4 * rg;
+      const float* kr = ks + tt * DMAX + 4 * rg;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int m = 0; m < NG; ++m) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + 16 * m);
+        const float4 q4 = *reinterpret_cast<const float4*>(qr + 16 * m);
+        S[4 * m] = fmaf(k4.x, vj, lam * S[4 * m]);
+        S[4 * m + 1] = fmaf(k4.y, vj, lam * S[4 * m + 1]);
+        S[4 * m + 2] = fmaf(k4.z, vj, lam * S[4 * m + 2]);
+        S[4 * m + 3] = fmaf(k4.w, vj, lam * S[4 * m + 3]);
+        o0 = fmaf(q4.x, S[4 * m], o0); o1 = fmaf(q4.y, S[4 * m + 1], o1);
+        o2 = fmaf(q4.z, S[4 * m + 2], o2); o3 = fmaf(q4.w, S[4 * m + 3], o3);
+      }
+      float o = (o0 + o1) + (o2 + o3);
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (live && rg == 0) out[((size_t)row0 + t0 + tt) * heads * vdim + h * vdim + j] = o;
+    }
+    __syncthreads();
+  }
+  if (live) {
+#pragma unroll
+    for (int m = 0; m < NG; ++m)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = 4 * (m * RG + rg) + e;
+        if (i < dim) st[(size_t)i * vdim + j] = S[m * 4 + e];
+      }
+  }
+}
+
+template <typename T, int DMAX>
+static int launch_lightning(float* out, float* state, const void* proj, int ld, int q_col0, int k_col0, int v_col0,
+                            const float* decay, const int32_t* segs, int n_segs, int heads, int dim, int vdim,
+                            cudaStream_t st) {
+  constexpr int CH = 16;
+  // value columns per CTA: 64 for prompt-sized work, fewer while (segment, head, slice) CTAs do not fill the SMs
+  int vt = 64;
+  while (vt > 8 && (vt / 2 >= vdim || (long long)n_segs * heads * cdiv(vdim, vt) < 148)) vt /= 2;
+  const size_t smem = sizeof(float) * CH * (2 * DMAX + vt);
+  return launch_pdl("lightning", lightning_kernel<T, DMAX, CH>, dim3(n_segs, heads, cdiv(vdim, vt)), dim3(vt * 4), smem, st,
+                    out, state, (const T*)proj, ld, q_col0, k_col0, v_col0, decay, segs, heads, dim, vdim);
+}
+
 template <int DMAX, int CH>
 static int launch_delta(float* out, float* state, const float* rec, const int32_t* segs, int n_segs, int heads, int dim,
                         cudaStream_t st) {
@@ -322,6 +435,22 @@ extern "C" int pg_headnorm_gate(void* out, int ld_out, const float* o, const voi
     return launch_pdl("headnorm_gate", headnorm_gate_kernel<T>, dim3(cdiv((long long)n_tokens * heads, warps)),
                       dim3(warps * 32), 0, (cudaStream_t)stream, (T*)out, ld_out, o, (const T*)w, (const T*)gate, ld_gate,
                       n_tokens, heads, dim, eps, out_scale, pairs);
+  });
+  return PG_OK;
+}
+
+extern "C" int pg_lightning_attention(float* out, float* state, const void* proj, int ld, int q_col0, int k_col0,
+                                      int v_col0, const float* decay, const int32_t* segs, int n_segs, int heads,
+                                      int dim, int vdim, int dtype, void* stream) {
+  if (n_segs <= 0) return PG_OK;
+  PG_REQUIRE(out && state && proj && decay && segs, "lightning_attention: bad arguments");
+  PG_REQUIRE(dim > 0 && dim <= 256 && vdim > 0, "lightning_attention: key size %d (1..256), value size %d", dim, vdim);
+  cudaStream_t st = (cudaStream_t)stream;
+  PG_DISPATCH_DTYPE(dtype, T, {
+    if (dim <= 32) return launch_lightning<T, 32>(out, state, proj, ld, q_col0, k_col0, v_col0, decay, segs, n_segs, heads, dim, vdim, st);
+    if (dim <= 64) return launch_lightning<T, 64>(out, state, proj, ld, q_col0, k_col0, v_col0, decay, segs, n_segs, heads, dim, vdim, st);
+    if (dim <= 128) return launch_lightning<T, 128>(out, state, proj, ld, q_col0, k_col0, v_col0, decay, segs, n_segs, heads, dim, vdim, st);
+    return launch_lightning<T, 256>(out, state, proj, ld, q_col0, k_col0, v_col0, decay, segs, n_segs, heads, dim, vdim, st);
   });
   return PG_OK;
 }

@@ -14,6 +14,7 @@ LIB_PATH = os.environ.get("PG_LIB_PATH") or os.path.join(_HERE, "libpg_b200.so")
 
 PG_F32, PG_BF16, PG_F16 = 0, 1, 2
 EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RES, EPI_RES, EPI_GEGLU, EPI_SWIGLU = 0, 1, 2, 3, 4, 5, 6
+GLU_NONE, GLU_SILU, GLU_CLAMPED = 0, 1, 2      # pairings of pg_moe_gemm_act
 MAX_DECODE_BATCH = 8            # rows one launch of the GEMV kernels can take
 # from this batch size on the decode step runs the tensor-core (swap-AB skinny GEMM) path: the GEMV kernels turn
 # ALU-bound as rows are added (batch 8: 4.34 ms/step vs ~2 ms), tools/kernel_sweep.py SWEEP_B=...
@@ -90,6 +91,18 @@ SIGNATURES = {
     "pg_moe_gemm": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],
     "pg_gather_rows": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp],
     "pg_moe_combine": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    # sigmoid / grouped router, named pairings, lightning attention, latent attention
+    "pg_moe_gemm_act": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _i, _vp],
+    "pg_moe_route_grouped": [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "pg_moe_combine_out": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "pg_glu_clamped": [_vp, _vp, _i, _i, _f, _f, _i, _vp],
+    "pg_lightning_attention": [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "pg_latent_prep": [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _f, _f, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _vp],
+    "pg_rotary_cols": [_vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _i, _i, _vp],
+    "pg_head_gemm": [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "pg_attention_ragged_sink": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i,
+                                 _i, _f, _i, _i, _vp, _i, _vp, _vp, _f, _vp, _ll, _i, _vp],
+    "pg_concat_cast": [_vp, _vp, _vp, _i, _i, _i, _vp],
 }
 _RESTYPE = {"pg_last_error": C.c_char_p, "pg_launch_count": _ull, "pg_decode_attention_ws_floats": _ll,
             "pg_delta_record_floats": _ll}

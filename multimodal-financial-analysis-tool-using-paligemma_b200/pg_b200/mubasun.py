@@ -133,7 +133,6 @@ class MubasunEngine(RaggedEngine):
         self._init_common(device=device, dtype=dtype, page_size=page_size, gemm_impl=gemm_impl)
         self.max_positions = self.cfg.max_positions
         self.moe_impl = int(os.environ.get("PG_MOE_IMPL", moe_impl))
-        self.moe_tc_min_pairs = int(os.environ.get("PG_MOE_TC_MIN_PAIRS", "1"))
         self._repack(weights)
         for w, lc in zip(self.layers, self.cfg.layers):
             npj = w["proj"].shape[0]
@@ -295,27 +294,7 @@ class MubasunEngine(RaggedEngine):
             cabi.check(L.pg_moe_route(ptr(idx), ptr(wts), ptr(sg), ptr(h), h.stride(0), ptr(w["router"]),
                                       ptr(w["correction"]), ptr(w.get("s_sg")), T, D, E + ml.identity, ml.top,
                                       ml.router_scale, self.dt, st), "moe_route")
-        offsets = self._new(E + 1, dtype=torch.int32)
-        rows, pos = self._new(P, dtype=torch.int32), self._new(P, dtype=torch.int32)
-        with tm("moe_sort"):
-            cabi.check(L.pg_moe_sort(ptr(offsets), ptr(rows), ptr(pos), ptr(idx), P, ml.top, E, st), "moe_sort")
-        act, y = self._new(P, ml.ff), self._new(P, D)
-        # prompt-sized steps: the rows are gathered into expert order once and both GEMMs run on the tensor cores;
-        # a handful of pairs (decode steps) read h through the row map in the fp32-FMA kernel
-        tc = (self.dtype != torch.float32 and self.moe_impl != 1 and P >= self.moe_tc_min_pairs
-              and D % 8 == 0 and ml.ff % 8 == 0)
-        a, row_map, impl = h, rows, 1
-        if tc:
-            a, row_map, impl = self._new(P, D), None, 2
-            with tm("moe_gather"):
-                cabi.check(L.pg_gather_rows(ptr(a), ptr(h), h.stride(0), ptr(rows), ptr(offsets[E:]), P, D, self.dt, st),
-                           "gather_rows")
-        with tm("moe_gate_up"):
-            cabi.check(L.pg_moe_gemm(ptr(act), ml.ff, ptr(a), a.stride(0), ptr(row_map), ptr(w["gu"]), ptr(offsets), P, E,
-                                     ml.ff, D, 1, impl, ptr(self.err_flag), self.dt, st), "moe_gemm gate/up")
-        with tm("moe_down"):
-            cabi.check(L.pg_moe_gemm(ptr(y), D, ptr(act), ml.ff, None, ptr(w["dn"]), ptr(offsets), P, E, D, ml.ff, 0,
-                                     impl, ptr(self.err_flag), self.dt, st), "moe_gemm down")
+        y, pos = self._moe_experts(h, idx, E, ml.top, ml.ff, w["gu"], w["dn"])
         so = None
         if ml.shared_ff:
             with tm("shared_gate_up"):

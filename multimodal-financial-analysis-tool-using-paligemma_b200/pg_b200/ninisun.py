@@ -39,39 +39,11 @@ import torch
 
 from . import _cabi as cabi
 from ._cabi import ptr
-from .ragged_engine import RaggedEngine, StepInputs
+from .ragged_engine import RaggedEngine, RotaryCfg, StepInputs, _stack_rows
 from .registry import register
 
 DECAY_SCALE = math.exp(-0.5)      # w = exp(-DECAY_SCALE * sigmoid(.)): the design's fixed decay range
 KEY_EPS = 1e-6                    # inside the root of the unit key's length
-
-
-@dataclass
-class RotaryCfg:
-    dims: int
-    base: float
-    scaling: Optional[dict] = None       # YaRN: factor, original, fast, slow
-
-    def table(self):
-        """(frequencies float64 [dims / 2], magnitude): angle of pair i at position p = p * f_i; with YaRN scaling the
-        slow pairs are interpolated (f / factor), the fast ones kept, a linear ramp in between, and cos / sin are
-        both multiplied by 0.1 ln(factor) + 1."""
-        i = torch.arange(self.dims // 2, dtype=torch.float64)
-        f = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / self.dims)
-        mag = 1.0
-        sc = self.scaling
-        if sc:
-            factor, orig = float(sc["factor"]), float(sc["original"])
-
-            def pair_of(turns: float) -> float:     # the pair index that makes `turns` full turns over `orig` positions
-                return self.dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
-
-            lo = max(math.floor(pair_of(float(sc["fast"]))), 0)
-            hi = min(math.ceil(pair_of(float(sc["slow"]))), self.dims - 1)
-            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
-            f = f / factor * ramp + f * (1.0 - ramp)
-            mag = 0.1 * math.log(factor) + 1.0
-        return f, mag
 
 
 @dataclass
@@ -150,21 +122,6 @@ class NinisunConfig:
             raise ValueError("layers that mix values must agree on their value width")
         return NinisunConfig(vocab=int(cfg["vocab"]), width=int(cfg["width"]), eps=float((cfg.get("norm") or {})["eps"]),
                              layers=layers)
-
-
-def _stack_rows(parts, device, dtype, align=8):
-    """Concatenate [rows_i, K] matrices with every part starting at a multiple of `align` rows (zero rows between),
-    so that the columns of the fused projection's output start aligned.  Returns (matrix, {name: first row})."""
-    rows, at, n = [], {}, 0
-    for name, t in parts:
-        at[name] = n
-        rows.append(t)
-        n += t.shape[0]
-        pad = (-n) % align
-        if pad:
-            rows.append(torch.zeros((pad, t.shape[1]), dtype=dtype, device=device))
-            n += pad
-    return torch.cat(rows, 0).contiguous(), at
 
 
 @register("Ninisun")

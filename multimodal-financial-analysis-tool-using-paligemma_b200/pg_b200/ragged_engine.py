@@ -18,6 +18,7 @@ Inputs of a step on the device (one int32 buffer, `StepInputs` names its parts):
 """
 from __future__ import annotations
 
+import math
 import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
@@ -42,6 +43,51 @@ class StepInputs:
     n_segs: int
     tiles: torch.Tensor          # int32 [4 * n_tiles]
     n_tiles: int
+
+
+@dataclass
+class RotaryCfg:
+    dims: int
+    base: float
+    scaling: Optional[dict] = None       # YaRN: factor, original, fast, slow
+
+    def table(self):
+        """(frequencies float64 [dims / 2], magnitude): angle of pair i at position p = p * f_i; with YaRN scaling the
+        slow pairs are interpolated (f / factor), the fast ones kept, a linear ramp in between, and cos / sin are
+        both multiplied by 0.1 ln(factor) + 1."""
+        i = torch.arange(self.dims // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / self.dims)
+        mag = 1.0
+        sc = self.scaling
+        if sc:
+            factor, orig = float(sc["factor"]), float(sc["original"])
+
+            def pair_of(turns: float) -> float:     # the pair index that makes `turns` full turns over `orig` positions
+                return self.dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+
+            lo = max(math.floor(pair_of(float(sc["fast"]))), 0)
+            hi = min(math.ceil(pair_of(float(sc["slow"]))), self.dims - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+            mag = 0.1 * math.log(factor) + 1.0
+        return f, mag
+
+
+
+def _stack_rows(parts, device, dtype, align=8):
+    """Concatenate [rows_i, K] matrices with every part starting at a multiple of `align` rows (zero rows between),
+    so that the columns of the fused projection's output start aligned.  Returns (matrix, {name: first row})."""
+    rows, at, n = [], {}, 0
+    for name, t in parts:
+        at[name] = n
+        rows.append(t)
+        n += t.shape[0]
+        pad = (-n) % align
+        if pad:
+            rows.append(torch.zeros((pad, t.shape[1]), dtype=dtype, device=device))
+            n += pad
+    return torch.cat(rows, 0).contiguous(), at
+
 
 
 class RaggedEngine(PagePool):
@@ -71,6 +117,9 @@ class RaggedEngine(PagePool):
         # steps of at least this many tokens run the tcgen05 attention kernel (layers whose head sizes it takes)
         self.attn_tc_min_tokens = int(os.environ.get("PG_RAGGED_ATTN_TC_MIN", "48"))
         self._attn_tc_any = False
+        # expert GEMMs: 0 = tensor cores where the sizes allow, 1 = the fp32-FMA kernel; pairs from which they are taken
+        self.moe_impl = int(os.environ.get("PG_MOE_IMPL", "0"))
+        self.moe_tc_min_pairs = int(os.environ.get("PG_MOE_TC_MIN_PAIRS", "1"))
         self._graphs: Dict[tuple, tuple] = {}
         self._op_timing = os.environ.get("PG_OP_TIMING", "0") == "1"
         self._op_events: List[tuple] = []
@@ -123,6 +172,37 @@ class RaggedEngine(PagePool):
         cabi.check(L.pg_gemm(ptr(out), ptr(a), ptr(w), None, None, M, N, K, a.stride(0), w.stride(0), out.stride(0), 0, 0,
                              epi, 1 if out_f32 else 0, self.gemm_impl, self.dt, st), "gemm")
         return out
+
+    def _moe_experts(self, h: torch.Tensor, idx: torch.Tensor, n_experts: int, top: int, ff: int, w_gu: torch.Tensor,
+                     w_dn: torch.Tensor, act: int = cabi.GLU_SILU, limit: float = 0.0):
+        """The routed experts' feed-forward of a token batch: the (token, expert) pairs `idx` [T * top] are grouped by
+        expert, both expert GEMMs run grouped (w_gu [E, 2 ff, D] with the pairing `act` in its epilogue, w_dn
+        [E, D, ff]).  Returns (y [pairs, D] in grouped order, pair_pos [T * top]: the row of every pair in y, -1 for
+        an index >= n_experts).  Prompt-sized steps gather the rows into expert order once and run on the tensor
+        cores; a handful of pairs read h through the row map in the fp32-FMA kernel."""
+        L, st, tm = cabi.lib(), cabi.stream(), self._tm
+        T, D = h.shape
+        P, E = T * top, n_experts
+        offsets = self._new(E + 1, dtype=torch.int32)
+        rows, pos = self._new(P, dtype=torch.int32), self._new(P, dtype=torch.int32)
+        with tm("moe_sort"):
+            cabi.check(L.pg_moe_sort(ptr(offsets), ptr(rows), ptr(pos), ptr(idx), P, top, E, st), "moe_sort")
+        act_out, y = self._new(P, ff), self._new(P, D)
+        tc = (self.dtype != torch.float32 and self.moe_impl != 1 and P >= self.moe_tc_min_pairs
+              and D % 8 == 0 and ff % 8 == 0)
+        a, row_map, impl = h, rows, 1
+        if tc:
+            a, row_map, impl = self._new(P, D), None, 2
+            with tm("moe_gather"):
+                cabi.check(L.pg_gather_rows(ptr(a), ptr(h), h.stride(0), ptr(rows), ptr(offsets[E:]), P, D, self.dt, st),
+                           "gather_rows")
+        with tm("moe_gate_up"):
+            cabi.check(L.pg_moe_gemm_act(ptr(act_out), ff, ptr(a), a.stride(0), ptr(row_map), ptr(w_gu), ptr(offsets), P, E,
+                                         ff, D, act, limit, impl, ptr(self.err_flag), self.dt, st), "moe_gemm gate/up")
+        with tm("moe_down"):
+            cabi.check(L.pg_moe_gemm_act(ptr(y), D, ptr(act_out), ff, None, ptr(w_dn), ptr(offsets), P, E, D, ff,
+                                         cabi.GLU_NONE, 0.0, impl, ptr(self.err_flag), self.dt, st), "moe_gemm down")
+        return y, pos
 
     # ------------------------------------------------------------------ one step
     @staticmethod

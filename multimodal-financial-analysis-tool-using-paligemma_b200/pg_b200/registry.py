@@ -33,7 +33,8 @@ def architectures() -> List[str]:
 
 
 def _load_builtin() -> None:
-    from . import mubasun  # noqa: F401  (registers itself)
+    from . import birizen  # noqa: F401  (registers itself)
+    from . import mubasun  # noqa: F401
     from . import ninisun  # noqa: F401
     from . import engine   # noqa: F401
 
