@@ -460,6 +460,15 @@ int pg_attention_ragged_sink(void* out, int ld_out, const void* q, int ld_q, con
                              const float* head_bias, const float* sink, float out_scale, float* ws, long long ws_floats,
                              int dtype, void* stream);
 int pg_concat_cast(void* out, const float* a, const float* b, int rows, int D, int dtype, void* stream);
+/* pg_attention_ragged_tc_ex with explicit row strides of the two pools (0: packed; multiples of 8 elements) and the
+ * softmax sink of pg_attention_ragged_sink. */
+int pg_attention_ragged_tc_sink(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
+                                long long pool_rows, const int32_t* page_table, int pt_stride, int page_size,
+                                const int32_t* tiles, int n_tiles, int n_tokens, int n_heads, int n_kv_heads, int dim,
+                                int vdim, float scale, int window, int keep_first, const float* slopes,
+                                int sigmoid_weights, const float* head_bias, const float* sink, float out_scale,
+                                int* err_flag, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

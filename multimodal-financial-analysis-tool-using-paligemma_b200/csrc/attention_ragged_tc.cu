@@ -56,6 +56,7 @@ struct WinParams {
   const float* head_bias;
   int gate_per_head;
   float out_scale;
+  const float* sink;             // per query head: exp(sink[h]) joins the softmax denominator (NULL: none)
 };
 
 template <typename T>
@@ -217,6 +218,7 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     }
     if (ok && wait_lim(bar_o, (n_tiles - 1) & 1, fail)) {
       tc_fence_after();
+      if (p.sink && !sig) l += __expf(p.sink[h] - m);              // a logit without key or value, counted once
       float inv = (sig ? 1.f : 1.f / l) * p.out_scale;
       const size_t trow = (size_t)row0 + r;
       T* orow = reinterpret_cast<T*>(p.out) + trow * p.ld_out + (size_t)h * p.vdim;
@@ -270,14 +272,18 @@ extern "C" int pg_attention_ragged_tc_ok(int dim, int vdim, int page_size, int l
   return tc::encode_fn() != nullptr ? 1 : 0;
 }
 
-extern "C" int pg_attention_ragged_tc_ex(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
-                                         int gate_per_head, const void* k_pool, const void* v_pool, long long pool_rows,
-                                         const int32_t* page_table, int pt_stride, int page_size, const int32_t* tiles,
-                                         int n_tiles, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
-                                         float scale, int window, int keep_first, const float* slopes,
-                                         int sigmoid_weights, const float* head_bias, float out_scale, int* err_flag,
-                                         int dtype, void* stream) {
+extern "C" int pg_attention_ragged_tc_sink(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                           int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
+                                           long long pool_rows, const int32_t* page_table, int pt_stride, int page_size,
+                                           const int32_t* tiles, int n_tiles, int n_tokens, int n_heads, int n_kv_heads,
+                                           int dim, int vdim, float scale, int window, int keep_first,
+                                           const float* slopes, int sigmoid_weights, const float* head_bias,
+                                           const float* sink, float out_scale, int* err_flag, int dtype, void* stream) {
   if (n_tiles <= 0) return PG_OK;
+  if (ld_k <= 0) ld_k = n_kv_heads * dim;
+  if (ld_v <= 0) ld_v = n_kv_heads * vdim;
+  PG_REQUIRE(ld_k >= n_kv_heads * dim && ld_v >= n_kv_heads * vdim && ld_k % 8 == 0 && ld_v % 8 == 0,
+             "attention_ragged_tc: pool rows of %d / %d elements", ld_k, ld_v);
   PG_REQUIRE(pg_attention_ragged_tc_ok(dim, vdim, page_size, ld_q, ld_out, (gate && !gate_per_head) ? ld_gate : 8, dtype),
              "attention_ragged_tc: unsupported problem (dim %d vdim %d page %d dtype %d)", dim, vdim, page_size, dtype);
   PG_REQUIRE(n_heads % n_kv_heads == 0, "attention_ragged_tc: heads %d / kv heads %d", n_heads, n_kv_heads);
@@ -287,12 +293,12 @@ extern "C" int pg_attention_ragged_tc_ex(void* out, int ld_out, const void* q, i
   const bool bf = dtype == PG_BF16;
   CUtensorMap mq, mk, mv;
   PG_REQUIRE(tc::make_map_2d(&mq, q, n_tokens, (long long)n_heads * dim, ld_q, tc::WQ, bf) &&
-                 tc::make_map_2d(&mk, k_pool, pool_rows, (long long)n_kv_heads * dim, (long long)n_kv_heads * dim, tc::WK, bf) &&
-                 tc::make_map_2d(&mv, v_pool, pool_rows, (long long)n_kv_heads * vdim, (long long)n_kv_heads * vdim, tc::WK, bf),
+                 tc::make_map_2d(&mk, k_pool, pool_rows, (long long)n_kv_heads * dim, (long long)ld_k, tc::WK, bf) &&
+                 tc::make_map_2d(&mv, v_pool, pool_rows, (long long)n_kv_heads * vdim, (long long)ld_v, tc::WK, bf),
              "attention_ragged_tc: cuTensorMapEncodeTiled failed");
   tc::WinParams p = {out, ld_out, gate, ld_gate, tiles, page_table, pt_stride, n_heads, n_heads / n_kv_heads, dim, vdim,
                      scale, window, slopes, err_flag, keep_first, sigmoid_weights ? 1 : 0, head_bias,
-                     gate_per_head ? 1 : 0, out_scale};
+                     gate_per_head ? 1 : 0, out_scale, sink};
   const size_t smem = 1024 + (size_t)tc::WQ * dim * 2 + 2 * (size_t)tc::WK * dim * 2 + (size_t)tc::WK * vdim * 2 +
                       (size_t)tc::WQ * tc::WK * 2 + 72 + 16;
   cudaStream_t st = (cudaStream_t)stream;
@@ -307,6 +313,19 @@ extern "C" int pg_attention_ragged_tc_ex(void* out, int ld_out, const void* q, i
   PG_REQUIRE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
              "attention_ragged_tc: cannot reserve %zu B of shared memory", smem);
   return launch_tc("attention_ragged_tc", kern, grid, dim3(256), smem, 1, false, st, mq, mk, mv, p);
+}
+
+extern "C" int pg_attention_ragged_tc_ex(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                         int gate_per_head, const void* k_pool, const void* v_pool, long long pool_rows,
+                                         const int32_t* page_table, int pt_stride, int page_size, const int32_t* tiles,
+                                         int n_tiles, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
+                                         float scale, int window, int keep_first, const float* slopes,
+                                         int sigmoid_weights, const float* head_bias, float out_scale, int* err_flag,
+                                         int dtype, void* stream) {
+  return pg_attention_ragged_tc_sink(out, ld_out, q, ld_q, gate, ld_gate, gate_per_head, k_pool, 0, v_pool, 0, pool_rows,
+                                     page_table, pt_stride, page_size, tiles, n_tiles, n_tokens, n_heads, n_kv_heads, dim,
+                                     vdim, scale, window, keep_first, slopes, sigmoid_weights, head_bias, nullptr, out_scale,
+                                     err_flag, dtype, stream);
 }
 
 extern "C" int pg_attention_ragged_tc(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,

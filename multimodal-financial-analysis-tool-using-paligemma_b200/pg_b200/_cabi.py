@@ -103,6 +103,8 @@ SIGNATURES = {
     "pg_attention_ragged_sink": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i,
                                  _i, _f, _i, _i, _vp, _i, _vp, _vp, _f, _vp, _ll, _i, _vp],
     "pg_concat_cast": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "pg_attention_ragged_tc_sink": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i,
+                                    _i, _i, _f, _i, _i, _vp, _i, _vp, _vp, _f, _vp, _i, _vp],
 }
 _RESTYPE = {"pg_last_error": C.c_char_p, "pg_launch_count": _ull, "pg_decode_attention_ws_floats": _ll,
             "pg_delta_record_floats": _ll}

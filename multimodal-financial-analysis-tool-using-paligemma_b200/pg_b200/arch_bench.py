@@ -529,3 +529,199 @@ def run_ninisun(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048
         torch.cuda.empty_cache()
     result["gpu_launches"] = int(cabi.launch_count() - launches0)
     return result
+
+
+# ------------------------------------------------------------------ Birizen beside the MoE Mubasun and Ninisun of equal size
+BIRIZEN_SIZES = {
+    # lightning layers: heads x dim / vdim; latent layers: heads x (dim plain + rot_dim rotated) / vdim over latents of
+    # q_rank / kv_rank; experts x ff (top, groups kept of groups), shared ff; layers 2..3 run twice
+    "w1024": dict(width=1024, layers=4, heads=8, dim=128, vdim=128, rot_dim=64, q_rank=384, kv_rank=192, experts=8, top=2,
+                  groups=4, keep=2, expert_ff=1024, shared_ff=1024, loop=(2, 4, 2), vocab=32000),
+    "w2048": dict(width=2048, layers=4, heads=16, dim=128, vdim=128, rot_dim=64, q_rank=768, kv_rank=192, experts=16, top=2,
+                  groups=4, keep=2, expert_ff=2048, shared_ff=2048, loop=(2, 4, 2), vocab=32000),
+}
+
+
+def birizen_config(s: dict) -> dict:
+    """lightning, latent, lightning, latent; the last two layers run `times` times (every branch is on the path)."""
+    layers = []
+    for i in range(s["layers"]):
+        mlp = {"kind": "moe", "expert": {"ff": s["expert_ff"], "limit": 7.0}, "shared": {"ff": s["shared_ff"], "limit": 7.0},
+               "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": s["groups"], "keep": s["keep"]}}}
+        if i % 2 == 0:
+            H = s["heads"]
+            mixer = {"heads": H, "dim": s["dim"], "vdim": s["vdim"], "decay": [1.0 - 2.0 ** (-5 - 3 * h / H) for h in range(H)]}
+            layers.append({"type": "lightning", "mixer": mixer, "mlp": mlp})
+        else:
+            mixer = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["vdim"], "q_rank": s["q_rank"],
+                     "kv_rank": s["kv_rank"], "scale": 1.0 / math.sqrt(s["dim"] + s["rot_dim"]),
+                     "rot": {"dims": s["rot_dim"], "base": 10000.0,
+                             "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+            layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Birizen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "layers": layers,
+            "loop": dict(zip(("start", "stop", "times"), s["loop"]))}
+
+
+def random_birizen_weights(cfg: dict, device, dtype, seed=0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(seed)
+    D, out = cfg["width"], {}
+
+    def lin(name, o, i, gain=1.0):
+        out[name] = (torch.randn(o, i, generator=g, device=device) * (gain / math.sqrt(i))).to(dtype)
+
+    def vec(name, n, mean=1.0, std=0.1):
+        out[name] = (mean + std * torch.randn(n, generator=g, device=device)).to(dtype)
+
+    out["embed"] = torch.randn(cfg["vocab"], D, generator=g, device=device).to(dtype)
+    lin("loop.in", D, 2 * D)
+    out["loop.step"] = (0.1 * torch.randn(cfg["loop"]["times"], D, generator=g, device=device)).to(dtype)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        for n in ("norm1", "norm1b", "norm2", "norm2b"):
+            vec(p + n, D)
+        H = m["heads"]
+        if L["type"] == "lightning":
+            lin(p + "mix.q", H * m["dim"], D), lin(p + "mix.k", H * m["dim"], D), lin(p + "mix.v", H * m["vdim"], D)
+            lin(p + "mix.g", H * m["vdim"], D), lin(p + "mix.o", D, H * m["vdim"]), vec(p + "mix.norm", H * m["vdim"])
+        else:
+            lin(p + "mix.dq", m["q_rank"], D), vec(p + "mix.dq.norm", m["q_rank"])
+            lin(p + "mix.uq", H * (m["dim"] + m["rot_dim"]), m["q_rank"])
+            lin(p + "mix.dkv", m["kv_rank"] + m["rot_dim"], D), vec(p + "mix.dkv.norm", m["kv_rank"])
+            lin(p + "mix.uk", H * m["dim"], m["kv_rank"]), lin(p + "mix.uv", H * m["vdim"], m["kv_rank"])
+            vec(p + "mix.sink", H, 0.0, 1.0), lin(p + "mix.g", H * m["vdim"], D), lin(p + "mix.o", D, H * m["vdim"])
+        ml = L["mlp"]
+        for e in range(ml["router"]["experts"]):
+            lin(f"{p}mlp.e{e}.gate", ml["expert"]["ff"], D), lin(f"{p}mlp.e{e}.up", ml["expert"]["ff"], D)
+            lin(f"{p}mlp.e{e}.down", D, ml["expert"]["ff"])
+        lin(p + "mlp.router", ml["router"]["experts"], D, 2.0)
+        vec(p + "mlp.correction", ml["router"]["experts"], 0.0, 0.05)
+        lin(p + "mlp.shared.gate", ml["shared"]["ff"], D), lin(p + "mlp.shared.up", ml["shared"]["ff"], D)
+        lin(p + "mlp.shared.down", D, ml["shared"]["ff"])
+    vec("final.norm", D)
+    return out
+
+
+def _birizen_run_layers(s: dict, cfg: dict) -> List[dict]:
+    a, b, times = s["loop"]
+    order = list(range(a)) + list(range(a, b)) * times + list(range(b, s["layers"]))
+    return [cfg["layers"][i] for i in order]
+
+
+def birizen_work(s: dict, cfg: dict, T1: int, seqs: int) -> Dict[str, tuple]:
+    """name -> (FLOPs, bytes) of one step over `seqs` prompts of T1 tokens (bf16 operands, fp32 residual stream and
+    recurrent state), summed over the layer runs."""
+    T, D = T1 * seqs, s["width"]
+    H, dim, vdim, rot, qr, kr = s["heads"], s["dim"], s["vdim"], s["rot_dim"], s["q_rank"], s["kv_rank"]
+    E, top, F, S = s["experts"], s["top"], s["expert_ff"], s["shared_ff"]
+    w: Dict[str, List[float]] = {}
+
+    def add(name, flops, nbytes):
+        a = w.setdefault(name, [0.0, 0.0])
+        a[0] += flops
+        a[1] += nbytes
+
+    all_keys = seqs * T1 * (T1 + 1) // 2
+    add("norm", 0, (1 + s["loop"][2]) * T * D * (4 + 4 + 2))
+    add("loop_in", s["loop"][2] * 2 * T * 2 * D * D, s["loop"][2] * (T * D * (8 + 4 + 4) + 2 * 2 * D * D))
+    for L in _birizen_run_layers(s, cfg):
+        if L["type"] == "lightning":
+            nk, nv = H * dim, H * vdim
+            npj = 2 * nk + 2 * nv
+            add("proj", 2 * T * D * npj, 2 * (T * D + npj * D + T * npj))
+            add("lightning", 4 * T * H * dim * vdim, T * (2 * (2 * nk + nv) + 4 * nv))        # fp32 FMAs, not tensor work
+            add("headnorm_gate", 0, T * nv * (4 + 2 + 2))
+            add("o", 2 * T * nv * D, 2 * (T * nv + nv * D + T * D))
+        else:
+            hq, hv, ldq = H * (dim + rot), H * vdim, kr + rot
+            npj = qr + kr + rot + hv
+            add("proj", 2 * T * D * npj, 2 * (T * D + npj * D + T * npj))
+            add("latent_prep", 0, 2 * T * (2 * qr + 2 * (kr + rot)))
+            add("q_up", 2 * T * qr * hq, 2 * (T * qr + hq * qr + T * hq))
+            add("q_absorb", 2 * T * H * dim * kr, 2 * (T * hq + H * dim * kr + T * H * ldq))
+            add("latent_attention", 2 * all_keys * H * (ldq + kr), 2 * T * H * (ldq + kr) + 2 * T * ldq)
+            add("v_up_gate", 2 * T * H * kr * vdim, 2 * (T * H * kr + H * vdim * kr + 2 * T * hv))
+            add("o", 2 * T * hv * D, 2 * (T * hv + hv * D + T * D))
+        P = T * top
+        add("post_norm", 0, 2 * T * D * (2 + 4 + 4 + 2))
+        add("moe_route", 2 * T * D * E, 2 * T * D)
+        add("moe_sort", 0, 4 * 3 * P)
+        add("moe_gather", 0, 2 * 2 * P * D)
+        add("moe_gate_up", 2 * P * D * 2 * F, 2 * (P * D + E * 2 * F * D + P * F))
+        add("moe_down", 2 * P * F * D, 2 * (P * F + E * F * D + P * D))
+        add("shared_gate_up", 2 * T * D * 2 * S, 2 * (T * D + 2 * S * D + 2 * T * S + T * S))
+        add("shared_down", 2 * T * S * D, 2 * (T * S + S * D + T * D))
+        add("moe_combine", 0, 2 * P * D + T * D * (2 + 2))
+    add("head", 2 * seqs * D * s["vocab"], 2 * D * s["vocab"])
+    return {k: (v[0], v[1]) for k, v in w.items()}
+
+
+def _birizen_decode_bytes(s: dict, cfg: dict, B: int) -> float:
+    """Weight bytes one decode step of B tokens must stream (experts: at most B * top of them per MoE layer run)."""
+    D, n = s["width"], 0.0
+    H, dim, vdim, rot, qr, kr = s["heads"], s["dim"], s["vdim"], s["rot_dim"], s["q_rank"], s["kv_rank"]
+    for L in _birizen_run_layers(s, cfg):
+        if L["type"] == "lightning":
+            n += D * (2 * H * dim + 3 * H * vdim)
+        else:
+            n += D * (qr + kr + rot + 2 * H * vdim) + qr * H * (dim + rot) + H * kr * (dim + vdim)
+        n += min(s["experts"], B * s["top"]) * 3 * D * s["expert_ff"] + 3 * D * s["shared_ff"] + D * s["experts"]
+    n += s["loop"][2] * 2 * D * D + D * s["vocab"]
+    return 2.0 * n
+
+
+# (Birizen op, the like op) against the MoE Mubasun and against Ninisun at equal width
+BIRIZEN_LIKE_MUBASUN = [("proj", "proj"), ("loop_in", "proj"), ("q_up", "proj"), ("q_absorb", "proj"), ("v_up_gate", "o"),
+                        ("o", "o"), ("latent_prep", "qknorm_append"), ("latent_attention", "attention"),
+                        ("moe_route", "moe_route"), ("moe_gather", "moe_gather"), ("moe_gate_up", "moe_gate_up"),
+                        ("moe_down", "moe_down"), ("shared_gate_up", "shared_gate_up"), ("shared_down", "shared_down"),
+                        ("moe_combine", "moe_combine"), ("norm", "norm"), ("head", "head")]
+BIRIZEN_LIKE_NINISUN = [("lightning", "delta_rule"), ("headnorm_gate", "headnorm_gate"), ("post_norm", "post_norm")]
+
+
+@torch.no_grad()
+def run_birizen(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, prefill_seqs=4, context=1024,
+                decode_batches=(1, 8)) -> dict:
+    from .birizen import BirizenEngine
+    from .mubasun import MubasunEngine
+    from .ninisun import NinisunEngine
+    dev, dtype = torch.device("cuda:0"), torch.bfloat16
+    timer = _Timer()
+    result = {}
+    launches0 = cabi.launch_count()
+    pool = (max(max(decode_batches), prefill_seqs) + 1) * (max(prefill_tokens, context) + 256)
+    for name in sizes:
+        s = BIRIZEN_SIZES[name]
+        cfg = birizen_config(s)
+        eng = BirizenEngine(cfg, random_birizen_weights(cfg, dev, dtype), device=dev, dtype=dtype, kv_pool_tokens=pool)
+        row = {"size": s}
+        row.update(_measure_ragged(eng, s["vocab"], timer, steps, warmup, peaks, birizen_work(s, cfg, prefill_tokens, prefill_seqs),
+                                   lambda B: _birizen_decode_bytes(s, cfg, B), prefill_tokens, prefill_seqs, context,
+                                   decode_batches))
+        del eng
+        torch.cuda.empty_cache()
+        ms_ = SIZES[name]
+        mcfg = mubasun_config(ms_)
+        meng = MubasunEngine(mcfg, random_mubasun_weights(mcfg, dev, dtype), device=dev, dtype=dtype, kv_pool_tokens=pool)
+        mrow = _measure_ragged(meng, ms_["vocab"], timer, steps, warmup, peaks, mubasun_work(ms_, mcfg, prefill_tokens, prefill_seqs),
+                               lambda B: _decode_bytes(ms_, mcfg, B), prefill_tokens, prefill_seqs, context, decode_batches)
+        row["mubasun_equal_size"] = mrow
+        del meng
+        torch.cuda.empty_cache()
+        ns_ = NINISUN_SIZES[name]
+        ncfg = ninisun_config(ns_)
+        neng = NinisunEngine(ncfg, random_ninisun_weights(ncfg, ns_, dev, dtype), device=dev, dtype=dtype, kv_pool_tokens=pool)
+        nrow = _measure_ragged(neng, ns_["vocab"], timer, steps, warmup, peaks, ninisun_work(ns_, ncfg, prefill_tokens, prefill_seqs),
+                               lambda B: _ninisun_decode_bytes(ns_, ncfg), prefill_tokens, prefill_seqs, context, decode_batches)
+        row["ninisun_equal_size"] = nrow
+        del neng
+        torch.cuda.empty_cache()
+        cmpr = {}
+        for like, other in ((BIRIZEN_LIKE_MUBASUN, mrow), (BIRIZEN_LIKE_NINISUN, nrow)):
+            for a, bname in like:
+                if a in row["prefill_ops"] and bname in other["prefill_ops"]:
+                    fa, fb = row["prefill_ops"][a]["frac"], other["prefill_ops"][bname]["frac"]
+                    cmpr[a] = {"frac": fa, "like": bname, "like_frac": fb, "distance_ratio": round(fb / fa, 2) if fa > 0 else None}
+        row["like_for_like"] = cmpr
+        result[name] = row
+    result["gpu_launches"] = int(cabi.launch_count() - launches0)
+    return result

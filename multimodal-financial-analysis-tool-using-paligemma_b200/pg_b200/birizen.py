@@ -181,6 +181,12 @@ class BirizenEngine(RaggedEngine):
         self.runs = self.cfg.runs()
         self.needs_segments = any(self.cfg.layers[r.layer].kind == "lightning" for r in self.runs)
         self._repack(weights)
+        for w, lc in zip(self.layers, self.cfg.layers):     # prompt portions of latent layers whose sizes the tensor-core kernel takes
+            a = lc.mixer
+            w["attn_tc"] = lc.kind == "latent_attention" and bool(cabi.lib().pg_attention_ragged_tc_ok(
+                a.kv_rank + a.rot_dim, a.kv_rank, self.page_size, a.heads * (a.kv_rank + a.rot_dim), a.heads * a.kv_rank, 8,
+                self.dt))
+        self._attn_tc_any = any(w["attn_tc"] for w in self.layers)
         self._init_runtime(kv_pool_tokens)
         # one latent pool per RUN of a latent layer: a layer that runs twice keeps two caches
         self.c_pools: Dict[int, torch.Tensor] = {}
@@ -320,11 +326,18 @@ class BirizenEngine(RaggedEngine):
                                         a.rot_dim, ptr(w["freq"]), w["mag"], ptr(inp.pos), T, self.dt, st), "rotary_cols")
         ol = self._new(T, a.heads * a.kv_rank)
         with tm("latent_attention"):
-            cabi.check(L.pg_attention_ragged_sink(
-                ptr(ol), ol.stride(0), ptr(qa), qa.stride(0), None, 0, 0, ptr(pool), ldp, ptr(pool), ldp,
-                ptr(kv.page_table), kv.max_pages, self.page_size, ptr(inp.slot), ptr(inp.pos), T, a.heads, 1, ld_q,
-                a.kv_rank, a.scale, 0, 0, None, 0, None, ptr(w["sink"]), 1.0, ptr(self.attn_ws), self.attn_ws.numel(),
-                self.dt, st), "attention_ragged_sink")
+            if inp.n_tiles and w["attn_tc"]:
+                cabi.check(L.pg_attention_ragged_tc_sink(
+                    ptr(ol), ol.stride(0), ptr(qa), qa.stride(0), None, 0, 0, ptr(pool), ldp, ptr(pool), ldp,
+                    self.num_pages * self.page_size, ptr(kv.page_table), kv.max_pages, self.page_size, ptr(inp.tiles),
+                    inp.n_tiles, T, a.heads, 1, ld_q, a.kv_rank, a.scale, 0, 0, None, 0, None, ptr(w["sink"]), 1.0,
+                    ptr(self.err_flag), self.dt, st), "attention_ragged_tc_sink")
+            else:
+                cabi.check(L.pg_attention_ragged_sink(
+                    ptr(ol), ol.stride(0), ptr(qa), qa.stride(0), None, 0, 0, ptr(pool), ldp, ptr(pool), ldp,
+                    ptr(kv.page_table), kv.max_pages, self.page_size, ptr(inp.slot), ptr(inp.pos), T, a.heads, 1, ld_q,
+                    a.kv_rank, a.scale, 0, 0, None, 0, None, ptr(w["sink"]), 1.0, ptr(self.attn_ws),
+                    self.attn_ws.numel(), self.dt, st), "attention_ragged_sink")
         att = self._new(T, a.heads * a.vdim)
         with tm("v_up_gate"):
             cabi.check(L.pg_head_gemm(ptr(att), att.stride(0), a.vdim, ptr(ol), ol.stride(0), a.kv_rank, ptr(w["uv"]),

@@ -219,6 +219,46 @@ def test_latent_space_attention_with_sink(H, kvr, rot, new):
     _rows_close(got, want, 1e-5)
 
 
+@pytest.mark.parametrize("H,kvr,rot", [(4, 64, 64), (2, 192, 64), (8, 128, 0)])
+@pytest.mark.parametrize("tower", [None, 0, 63, 64, 200])
+def test_latent_space_attention_on_the_tensor_cores(H, kvr, rot, tower):
+    """Prompt portions (query tiles of up to 128 consecutive tokens of one sequence) through the tcgen05 kernel: value
+    rows that are a prefix of the key rows of one pool, the sink in the denominator; one far key that stands out."""
+    cabi, L, st = _lib()
+    dtype, dim, scale = torch.bfloat16, kvr + rot, 0.3
+    assert L.pg_attention_ragged_tc_ok(dim, kvr, PAGE, H * dim, H * kvr, 8, CT[dtype])
+    g = torch.Generator().manual_seed(29)
+    lens, new = [300, 70, 150], [170, 3, 150]
+    pg = Paged(lens, dim, 1, dtype)
+    sink = torch.randn(H, generator=g)
+    qs, want, tiles, row = [], [], [], 0
+    for s, (n, m) in enumerate(zip(lens, new)):
+        q, k = torch.randn(n, H, dim, generator=g), torch.randn(n, 1, dim, generator=g)
+        if tower is not None and tower < n:
+            k[tower, 0] = 30.0 * q[n - 1, 0] / scale / dim
+        q, k = q.to(dtype).float(), k.to(dtype).float()
+        pg.fill(s, k[:, 0], torch.zeros(n, 1))
+        o = O.sink_softmax_attention(q.to(F64), k.to(F64).expand(n, H, dim), k.to(F64)[..., :kvr].expand(n, H, kvr), scale,
+                                     sink.to(F64))
+        qs.append(q[n - m:].reshape(m, H * dim))
+        want.append(o[n - m:].reshape(m, H * kvr))
+        for t0 in range(0, m, 128):
+            tiles += [row + t0, min(128, m - t0), s, n - m + t0]
+        row += m
+    q_all = torch.cat(qs).to(dtype).cuda()
+    T = q_all.shape[0]
+    out = torch.zeros(T, H * kvr, dtype=dtype, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sk = sink.cuda()
+    cabi.check(L.pg_attention_ragged_tc_sink(out.data_ptr(), H * kvr, q_all.data_ptr(), H * dim, None, 0, 0, pg.k.data_ptr(), dim,
+                                             pg.k.data_ptr(), dim, pg.k.shape[0] * PAGE, pg.table.data_ptr(), pg.max_pages, PAGE,
+                                             _i32(tiles).data_ptr(), len(tiles) // 4, T, H, 1, dim, kvr, scale, 0, 0, None, 0,
+                                             None, sk.data_ptr(), 1.0, err.data_ptr(), CT[dtype], st))
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    _rows_close(out, torch.cat(want), 2e-2)
+
+
 @pytest.mark.parametrize("where", [0, 1, 63, 64, 65, 127, 128, 700, 1398, 1399])
 @pytest.mark.parametrize("new", [1, 2, 130])
 def test_one_far_key_among_many(where, new):
@@ -372,7 +412,11 @@ CONFIGS = {
 }
 NO_ROUTER = {"plain": O.make_config(width=96, vocab=90, loop=(1, 3, 2), layers=[
     O.layer(O.lightning(heads=3, dim=16, vdim=32), None), O.layer(O.latent(heads=4, dim=16, rot_dim=8, vdim=24, q_rank=40, kv_rank=48), None),
-    O.layer(O.lightning(heads=2, dim=24, vdim=24), None)])}
+    O.layer(O.lightning(heads=2, dim=24, vdim=24), None)]),
+    # latent sizes that the tensor-core attention takes (16-bit prompt portions of 48 tokens and more)
+    "tensor_core_sizes": O.make_config(width=128, vocab=90, loop=(0, 1, 2), layers=[
+        O.layer(O.latent(heads=4, dim=32, rot_dim=64, vdim=32, q_rank=64, kv_rank=64, scale=0.1, scaling=SC), None),
+        O.layer(O.lightning(heads=2, dim=32, vdim=32), None)])}
 _ORACLE_CACHE = {}
 
 
