@@ -427,10 +427,14 @@ int pg_glu_clamped(void* out, const void* gate_up, int rows, int F, float limit,
 /* ---- lightning attention: linear attention with a constant decay per head ------------------------------------------
  * Per head, state S [dim x vdim] in fp32 per sequence slot ([slots][heads][dim][vdim]); q, k, v = silu of the fused
  * projection's columns at q_col0 / k_col0 / v_col0 (heads x dim, heads x dim, heads x vdim):
- *   S <- decay[h] S + k v^T;  o = S^T q.   segs as for pg_delta_rule; out fp32 [n_tokens, heads * vdim]. */
-int pg_lightning_attention(float* out, float* state, const void* proj, int ld, int q_col0, int k_col0, int v_col0,
-                           const float* decay, const int32_t* segs, int n_segs, int heads, int dim, int vdim, int dtype,
-                           void* stream);
+ *   S <- decay[h] S + k v^T;  o = S^T q.   segs as for pg_delta_rule; out fp32 [n_tokens, heads * vdim].
+ * pg_lightning_prep writes rec: pg_lightning_record_floats(n_tokens, heads, dim, vdim) floats (the fp32 activations,
+ * one packed record [q | k | v] per (token, head)); pg_lightning_attention runs the recurrence over them. */
+long long pg_lightning_record_floats(int n_tokens, int heads, int dim, int vdim);
+int pg_lightning_prep(float* rec, const void* proj, int ld, int q_col0, int k_col0, int v_col0, int n_tokens, int heads,
+                      int dim, int vdim, int dtype, void* stream);
+int pg_lightning_attention(float* out, float* state, const float* rec, const float* decay, const int32_t* segs, int n_segs,
+                           int heads, int dim, int vdim, void* stream);
 
 /* ---- latent attention ------------------------------------------------------------------------------------------
  * pg_latent_prep: from the fused projection row [.. dq (q_rank) .. dkv (kv_rank + rot_dim) ..]:
@@ -452,6 +456,12 @@ int pg_rotary_cols(void* dst, int ld_dst, int dst_col0, int dst_head_stride, con
                    int n_tokens, int dtype, void* stream);
 int pg_head_gemm(void* out, int ldo, int out_head_stride, const void* A, int lda, int a_head_stride, const void* W,
                  const void* gate, int ld_gate, int n_rows, int heads, int N, int K, int dtype, void* stream);
+/* out[t, h*out_head_stride + n] = in[(h*n_rows + t)*N + n] (* sigmoid(gate[t, h*N + n])): rows grouped by head
+ * (pg_moe_gemm with the heads as groups) back into token rows. */
+int pg_head_gather(void* out, const void* in, int ld_in, int in_head_stride, int n_rows, int heads, int K, int dtype,
+                   void* stream);   /* out[(h*n_rows + t)*K + k] = in[t*ld_in + h*in_head_stride + k] */
+int pg_head_scatter(void* out, int ldo, int out_head_stride, const void* in, const void* gate, int ld_gate, int n_rows,
+                    int heads, int N, int dtype, void* stream);
 int pg_attention_ragged_sink(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
                              int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
                              const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,

@@ -22,7 +22,8 @@
 // same token and its neighbours, so the key / value rows they share are served by L1.
 //
 // attention_ragged_split_kernel: decode-sized batches (a handful of tokens): one CTA per (token, key/value head, key
-// slice) serves all query heads of the group from ONE read of every key and value row; the keys are split over key
+// slice) serves all query heads of the group (or a chunk of 8 / 4 / 2 of them, when the group is larger or the value
+// rows are wide) from ONE read of every key and value row; the keys are split over key
 // slices (CTAs) and over the warps of a CTA; the partial (max, sum, acc) triples are merged through shared memory
 // and, across slices, through a caller-owned fp32 workspace by attention_ragged_merge_kernel, always in a fixed
 // order.  A lane owns ceil(vdim / 32) contiguous value columns, fetched with one vector load per key.
@@ -247,7 +248,9 @@ __global__ void __launch_bounds__(128) attention_ragged_split_kernel(RagAttnPara
   pdl_wait();
   constexpr int PW = 2 + 32 * DPL;                     // floats of one partial
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const int t = blockIdx.x / p.G, g = blockIdx.x % p.G, h0 = g * R;
+  // R query heads per CTA: a key/value head's group of H / G query heads is cut into chunks of R (gv counts the chunks)
+  const int chunks = p.H / (p.G * R), gv = blockIdx.x % (p.G * chunks);
+  const int t = blockIdx.x / (p.G * chunks), g = gv / chunks, h0 = gv * R;
   float* qs = smem;                                    // [R][dim]
   float* part = smem + R * p.dim;                      // [warps][R][PW]
   const T* qr = reinterpret_cast<const T*>(p.q) + (size_t)t * p.ld_q + h0 * p.dim;
@@ -386,7 +389,7 @@ static int launch_split(const RagAttnParams& p, float* ws, int slices, cudaStrea
   const size_t smem = sizeof(float) * ((size_t)R * p.dim + (size_t)warps * R * (2 + 32 * DPL));
   const long long items = (long long)p.n_tokens * p.H;
   int rc = launch_pdl("attention_ragged_split", attention_ragged_split_kernel<T, DPL, R>,
-                      dim3((unsigned)(p.n_tokens * p.G), slices), dim3(warps * 32), smem, st, p, ws);
+                      dim3((unsigned)(p.n_tokens * (p.H / R)), slices), dim3(warps * 32), smem, st, p, ws);
   if (rc != PG_OK || slices == 1) return rc;
   return launch_pdl("attention_ragged_merge", attention_ragged_merge_kernel<T, DPL>, dim3(cdiv(items, 4)), dim3(128), 0,
                     st, p, (const float*)ws, slices);
@@ -396,11 +399,15 @@ template <typename T, int DPL>
 static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats, cudaStream_t st) {
   const long long items = (long long)p.n_tokens * p.H;
   static const int split_max = env_int("PG_RAGGED_SPLIT_MAX_ITEMS", 592);   // below 4 (token, head) pairs per SM
-  const int R = p.H / p.G;
-  const bool r_ok = R == 1 || R == 2 || (R == 4 && DPL <= 8) || (R == 8 && DPL <= 4);
-  if (items <= split_max && r_ok && (p.window <= 0 || p.window > 64)) {
+  // query heads that one CTA serves from one read of the key / value rows: the largest of 8, 4, 2, 1 that divides the
+  // group and keeps the accumulators (heads x value columns per lane) in registers
+  const int group = p.H / p.G;
+  int R = 1;
+  for (int r = 8; r > 1; r >>= 1)
+    if (group % r == 0 && r * DPL <= 64) { R = r; break; }
+  if (items <= split_max && (p.window <= 0 || p.window > 64)) {
     // key slices until about two CTAs per SM are busy; a slice holds at least 128 keys (one block per warp)
-    const long long ctas = (long long)p.n_tokens * p.G;
+    const long long ctas = (long long)p.n_tokens * (p.H / R);
     const int span = p.window > 0 ? p.window : 1 << 20;
     int slices = 1;
     while (slices < 32 && ctas * slices * 2 <= 296 && span / (slices * 2) >= 128 &&
@@ -409,8 +416,8 @@ static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats,
     switch (R) {
       case 1: return launch_split<T, DPL, 1>(p, ws, slices, st);
       case 2: return launch_split<T, DPL, 2>(p, ws, slices, st);
-      case 4: return launch_split<T, (DPL <= 8 ? DPL : 8), 4>(p, ws, slices, st);
-      default: return launch_split<T, (DPL <= 4 ? DPL : 4), 8>(p, ws, slices, st);
+      case 4: return launch_split<T, DPL, 4>(p, ws, slices, st);
+      default: return launch_split<T, (DPL <= 8 ? DPL : 8), 8>(p, ws, slices, st);
     }
   }
   const int warps = 8;

@@ -13,6 +13,8 @@
 //   head_gemm_kernel     (64x64 tiles)    out[t, h] = A[t, h] W_h^T for every head h at once (fp32 accumulation), with an
 //                                         optional sigmoid gate on the output: the absorption of W_uk into the queries
 //                                         and the value expansion W_uv of the attended latents
+//   head_gather / head_scatter_kernel     token rows <-> rows grouped by head (the grouped tensor-core GEMM's layout), the
+//                                         way back with the same optional gate
 //   concat_cast_kernel                    [a | b] of two fp32 matrices as one model-dtype operand row
 #include "common.cuh"
 
@@ -196,6 +198,52 @@ head_gemv_kernel(T* __restrict__ out, int ldo, int o_hs, const T* __restrict__ A
   }
 }
 
+// Regrouping between token rows [M, heads, .] and rows grouped by head [heads, M, .] (the layout the grouped tensor-core
+// GEMM takes with the heads as its groups), 16 bytes per thread and access when the sizes allow:
+//   head_gather_kernel   out[(h M + t) K + k] = in[t ld_in + h in_hs + k]
+//   head_scatter_kernel  out[t ldo + h o_hs + n] = in[(h M + t) N + n] (* sigmoid(gate[t ldg + h N + n]))
+template <typename T, int V>
+__global__ void head_gather_kernel(T* __restrict__ out, const T* __restrict__ in, int ld_in, int in_hs, unsigned M,
+                                   unsigned heads, unsigned K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned kp = K / V, total = M * heads * kp;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const unsigned k = (i % kp) * V, r = i / kp, t = r % M, h = r / M;
+    const T* src = in + (size_t)t * ld_in + (size_t)h * in_hs + k;
+    T* dst = out + (size_t)r * K + k;
+    if constexpr (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    else *dst = *src;
+  }
+}
+
+template <typename T, int V>
+__global__ void head_scatter_kernel(T* __restrict__ out, int ldo, int o_hs, const T* __restrict__ in,
+                                    const T* __restrict__ gate, int ldg, unsigned M, unsigned heads, unsigned N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned np = N / V, total = M * heads * np;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const unsigned n = (i % np) * V, r = i / np, h = r % heads, t = r / heads;
+    const T* src = in + ((size_t)h * M + t) * N + n;
+    T* dst = out + (size_t)t * ldo + (size_t)h * o_hs + n;
+    float f[V], g[V];
+    if constexpr (V * sizeof(T) == 16) {
+      unpack<T>(*reinterpret_cast<const uint4*>(src), f);
+      if (gate) {
+        unpack<T>(*reinterpret_cast<const uint4*>(gate + (size_t)t * ldg + h * N + n), g);
+#pragma unroll
+        for (int j = 0; j < V; ++j) f[j] = rnd<T>(f[j]) * (1.f / (1.f + __expf(-g[j])));
+      }
+      *reinterpret_cast<uint4*>(dst) = pack<T>(f);
+    } else {
+      float v = to_f<T>(*src);
+      if (gate) v *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * ldg + h * N + n])));
+      *dst = from_f<T>(v);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ [a | b] of two fp32 matrices in the model dtype
 template <typename T>
 __global__ void concat_cast_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b,
@@ -268,6 +316,43 @@ extern "C" int pg_head_gemm(void* out, int ldo, int out_head_stride, const void*
     return launch_pdl("head_gemm", head_gemm_kernel<T>, dim3(cdiv(N, HG_BN), cdiv(n_rows, HG_BM), heads), dim3(HG_THREADS),
                       0, st, (T*)out, ldo, out_head_stride, (const T*)A, lda, a_head_stride, (const T*)W, (const T*)gate,
                       ld_gate, n_rows, N, K);
+  });
+  return PG_OK;
+}
+
+extern "C" int pg_head_gather(void* out, const void* in, int ld_in, int in_head_stride, int n_rows, int heads, int K,
+                              int dtype, void* stream) {
+  if (n_rows <= 0) return PG_OK;
+  PG_REQUIRE(out && in && heads > 0 && K > 0 && (long long)n_rows * heads * K < (1ll << 31), "head_gather: bad arguments");
+  PG_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = Vec<T>::N;
+    const bool vec = K % V == 0 && ld_in % V == 0 && in_head_stride % V == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)in % 16) == 0;
+    const long long total = (long long)n_rows * heads * (vec ? K / V : K);
+    const int blocks = (int)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+    if (vec)
+      return launch_pdl("head_gather", head_gather_kernel<T, V>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                        (const T*)in, ld_in, in_head_stride, (unsigned)n_rows, (unsigned)heads, (unsigned)K);
+    return launch_pdl("head_gather", head_gather_kernel<T, 1>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                      (const T*)in, ld_in, in_head_stride, (unsigned)n_rows, (unsigned)heads, (unsigned)K);
+  });
+  return PG_OK;
+}
+
+extern "C" int pg_head_scatter(void* out, int ldo, int out_head_stride, const void* in, const void* gate, int ld_gate,
+                               int n_rows, int heads, int N, int dtype, void* stream) {
+  if (n_rows <= 0) return PG_OK;
+  PG_REQUIRE(out && in && heads > 0 && N > 0 && (long long)n_rows * heads * N < (1ll << 31), "head_scatter: bad arguments");
+  PG_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = Vec<T>::N;
+    const bool vec = N % V == 0 && ldo % V == 0 && out_head_stride % V == 0 && (!gate || ld_gate % V == 0) &&
+                     ((uintptr_t)out % 16) == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)gate % 16) == 0;
+    const long long total = (long long)n_rows * heads * (vec ? N / V : N);
+    const int blocks = (int)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+    if (vec)
+      return launch_pdl("head_scatter", head_scatter_kernel<T, V>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                        ldo, out_head_stride, (const T*)in, (const T*)gate, ld_gate, (unsigned)n_rows, (unsigned)heads, (unsigned)N);
+    return launch_pdl("head_scatter", head_scatter_kernel<T, 1>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                      ldo, out_head_stride, (const T*)in, (const T*)gate, ld_gate, (unsigned)n_rows, (unsigned)heads, (unsigned)N);
   });
   return PG_OK;
 }

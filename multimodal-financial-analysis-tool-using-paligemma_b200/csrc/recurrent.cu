@@ -265,31 +265,58 @@ __global__ void headnorm_gate_kernel(T* __restrict__ out, int ld_out, const floa
 // Per head, with a state S [dim x vdim] (key channel i, value column j) kept in fp32 per sequence slot:
 //     q = silu(q_pre), k = silu(k_pre), v = silu(v_pre)          (pre-activations: the fused projection, model dtype)
 //     S <- decay_h S + k v^T,        o = S^T q
-// One CTA per (sequence segment, head, slice of VT value columns).  A thread owns a quarter of the rows of one value
-// column (the layout of the delta-rule kernel above: rows 4 (m RG + rg) + e), so a token costs one fused multiply-add
-// per state element for the update, one for the output, and two shuffle steps.  The activated q and k of CH tokens and
-// the slice's v are staged in shared memory as fp32; the state is read from and written back to the slot once per
-// launch, which makes a prompt portion and a single decoded token the same case and the result independent of where
-// the sequence was cut.
-template <typename T, int DMAX, int CH>
+// lightning_prep_kernel  (elementwise)  the activations in fp32, one packed record [q | k | v] per (token, head) with
+//                                       q, k padded to dp = dim rounded up to 4 floats and v to vp likewise (zeros).
+// lightning_kernel       (CTA per (sequence segment, head, slice of VT value columns)): a thread owns a quarter of
+//                                       the rows of one value column (the layout of the delta-rule kernel above: rows
+//                                       4 (m RG + rg) + e), so a token costs one fused multiply-add per state element
+//                                       for the update, one for the output, and two shuffle steps.  The records of
+//                                       the next CH tokens arrive by cp.async into the other half of a double buffer.
+//                                       The state is read from and written back to the slot once per launch, which
+//                                       makes a prompt portion and a single decoded token the same case and the
+//                                       result independent of where the sequence was cut.
+template <typename T>
+__global__ void lightning_prep_kernel(float* __restrict__ rec, const T* __restrict__ proj, int ld, int q_col0, int k_col0,
+                                      int v_col0, long long n_tokens, int heads, int dim, int vdim, int dp, int vp) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int rs = 2 * dp + vp;                       // floats of one record
+  // blockIdx.x: token; the CTA's threads walk the token's heads x record columns
+  const long long t = blockIdx.x;
+  const T* row = proj + t * ld;
+  float* out = rec + t * heads * rs;
+  for (int i = threadIdx.x; i < heads * rs; i += blockDim.x) {
+    const int h = i / rs, c = i - h * rs;
+    int col = -1;
+    if (c < dp) { if (c < dim) col = q_col0 + h * dim + c; }
+    else if (c < 2 * dp) { if (c - dp < dim) col = k_col0 + h * dim + c - dp; }
+    else if (c - 2 * dp < vdim) col = v_col0 + h * vdim + c - 2 * dp;
+    float a = 0.f;
+    if (col >= 0) {
+      a = to_f<T>(row[col]);
+      a = a * sigmoid_f(a);
+    }
+    out[i] = a;
+  }
+}
+
+template <int DMAX, int RG, int CH>
 __global__ void __launch_bounds__(256)
-lightning_kernel(float* __restrict__ out, float* __restrict__ state, const T* __restrict__ proj, int ld, int q_col0,
-                 int k_col0, int v_col0, const float* __restrict__ decay, const int32_t* __restrict__ segs, int heads,
-                 int dim, int vdim) {
-  constexpr int RG = 4, NG = DMAX / (4 * RG);
-  extern __shared__ __align__(16) float sh[];       // q [CH][DMAX] | k [CH][DMAX] | v [CH][VT]
+lightning_kernel(float* __restrict__ out, float* __restrict__ state, const float* __restrict__ rec,
+                 const float* __restrict__ decay, const int32_t* __restrict__ segs, int heads, int dim, int vdim, int dp,
+                 int vp) {
+  constexpr int NG = DMAX / (4 * RG);               // groups of four rows per thread (RG lanes share a value column)
+  extern __shared__ __align__(16) float sh[];       // [2][CH][q DMAX | k DMAX | v VT]
   pdl_launch_dependents();
   pdl_wait();
   const int32_t* sg = segs + 3 * (size_t)blockIdx.x;
   const int slot = sg[0], row0 = sg[1], n = sg[2];
   if (n <= 0) return;
-  const int VT = blockDim.x / RG;
-  float* qs = sh;
-  float* ks = sh + CH * DMAX;
-  float* vs = sh + 2 * CH * DMAX;
+  const int VT = blockDim.x / RG, RSZ = 2 * DMAX + VT, rs = 2 * dp + vp;
   const int h = blockIdx.y, j0 = blockIdx.z * VT, jl = threadIdx.x / RG, j = j0 + jl, rg = threadIdx.x % RG;
   const bool live = j < vdim;
   const float lam = decay[h];
+  for (int idx = threadIdx.x; idx < 2 * CH * RSZ; idx += blockDim.x) sh[idx] = 0.f;   // padding the copies never write
   float S[NG * 4];
   float* st = state + ((size_t)slot * heads + h) * dim * vdim;
 #pragma unroll
@@ -299,42 +326,37 @@ lightning_kernel(float* __restrict__ out, float* __restrict__ state, const T* __
       const int i = 4 * (m * RG + rg) + e;
       S[m * 4 + e] = (live && i < dim) ? st[(size_t)i * vdim + j] : 0.f;
     }
-  const int nv = min(VT, vdim - j0);
-  for (int t0 = 0; t0 < n; t0 += CH) {
+  __syncthreads();
+  const int qk_pieces = dp / 4, v_pieces = min(VT, vp - j0) / 4, pieces = 2 * qk_pieces + v_pieces;
+  auto fetch = [&](int t0, int buf) {               // records of tokens [t0, t0 + CH) of this head -> buffer buf
     const int nt = min(CH, n - t0);
-    for (int idx = threadIdx.x; idx < nt * DMAX; idx += blockDim.x) {
-      const int tt = idx / DMAX, c = idx % DMAX;
-      float a = 0.f, b = 0.f;
-      if (c < dim) {
-        const T* row = proj + (size_t)(row0 + t0 + tt) * ld + h * dim + c;
-        a = to_f<T>(row[q_col0]);
-        b = to_f<T>(row[k_col0]);
-        a = a * sigmoid_f(a);
-        b = b * sigmoid_f(b);
-      }
-      qs[idx] = a;
-      ks[idx] = b;
+    for (int idx = threadIdx.x; idx < nt * pieces; idx += blockDim.x) {
+      const int tt = idx / pieces, pc = idx % pieces;
+      const float* src = rec + (((size_t)row0 + t0 + tt) * heads + h) * (size_t)rs;
+      float* dst = sh + ((size_t)buf * CH + tt) * RSZ;
+      if (pc < qk_pieces) cp_async16(dst + pc * 4, src + pc * 4);
+      else if (pc < 2 * qk_pieces) cp_async16(dst + DMAX + (pc - qk_pieces) * 4, src + dp + (pc - qk_pieces) * 4);
+      else cp_async16(dst + 2 * DMAX + (pc - 2 * qk_pieces) * 4, src + 2 * dp + j0 + (pc - 2 * qk_pieces) * 4);
     }
-    for (int idx = threadIdx.x; idx < nt * VT; idx += blockDim.x) {
-      const int tt = idx / VT, c = idx % VT;
-      float a = 0.f;
-      if (c < nv) {
-        a = to_f<T>(proj[(size_t)(row0 + t0 + tt) * ld + v_col0 + h * vdim + j0 + c]);
-        a = a * sigmoid_f(a);
-      }
-      vs[idx] = a;
-    }
+    cp_async_commit();
+  };
+  fetch(0, 0);
+  int buf = 0;
+  for (int t0 = 0; t0 < n; t0 += CH, buf ^= 1) {
+    const int nt = min(CH, n - t0);
+    if (t0 + CH < n) { fetch(t0 + CH, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
     __syncthreads();
 #pragma unroll 2
     for (int tt = 0; tt < nt; ++tt) {
-      const float vj = vs[tt * VT + jl];
-      const float* qr = qs + tt * DMAX + 4 * rg;
-      const float* kr = ks + tt * DMAX + 4 * rg;
+      const float* r = sh + ((size_t)buf * CH + tt) * RSZ;
+      const float vj = r[2 * DMAX + jl];
+      const float* qr = r + 4 * rg;
+      const float* kr = r + DMAX + 4 * rg;
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int m = 0; m < NG; ++m) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kr + 16 * m);
-        const float4 q4 = *reinterpret_cast<const float4*>(qr + 16 * m);
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + 4 * RG * m);
+        const float4 q4 = *reinterpret_cast<const float4*>(qr + 4 * RG * m);
         S[4 * m] = fmaf(k4.x, vj, lam * S[4 * m]);
         S[4 * m + 1] = fmaf(k4.y, vj, lam * S[4 * m + 1]);
         S[4 * m + 2] = fmaf(k4.z, vj, lam * S[4 * m + 2]);
@@ -343,11 +365,11 @@ lightning_kernel(float* __restrict__ out, float* __restrict__ state, const T* __
         o2 = fmaf(q4.z, S[4 * m + 2], o2); o3 = fmaf(q4.w, S[4 * m + 3], o3);
       }
       float o = (o0 + o1) + (o2 + o3);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+      for (int sh_ = 1; sh_ < RG; sh_ <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh_);
       if (live && rg == 0) out[((size_t)row0 + t0 + tt) * heads * vdim + h * vdim + j] = o;
     }
-    __syncthreads();
+    __syncthreads();                                // every thread is done with this buffer before it is refilled
   }
   if (live) {
 #pragma unroll
@@ -360,17 +382,23 @@ lightning_kernel(float* __restrict__ out, float* __restrict__ state, const T* __
   }
 }
 
-template <typename T, int DMAX>
-static int launch_lightning(float* out, float* state, const void* proj, int ld, int q_col0, int k_col0, int v_col0,
-                            const float* decay, const int32_t* segs, int n_segs, int heads, int dim, int vdim,
-                            cudaStream_t st) {
-  constexpr int CH = 16;
-  // value columns per CTA: 64 for prompt-sized work, fewer while (segment, head, slice) CTAs do not fill the SMs
-  int vt = 64;
-  while (vt > 8 && (vt / 2 >= vdim || (long long)n_segs * heads * cdiv(vdim, vt) < 148)) vt /= 2;
-  const size_t smem = sizeof(float) * CH * (2 * DMAX + vt);
-  return launch_pdl("lightning", lightning_kernel<T, DMAX, CH>, dim3(n_segs, heads, cdiv(vdim, vt)), dim3(vt * 4), smem, st,
-                    out, state, (const T*)proj, ld, q_col0, k_col0, v_col0, decay, segs, heads, dim, vdim);
+template <int DMAX, int RG, int CH>
+static int launch_lightning(float* out, float* state, const float* rec, const float* decay, const int32_t* segs, int n_segs,
+                            int heads, int dim, int vdim, cudaStream_t st) {
+  const int dp = (dim + 3) / 4 * 4, vp = (vdim + 3) / 4 * 4;
+  // value columns per CTA: as many as 256 threads hold for prompt-sized work (few fat CTAs, about one per SM, beat
+  // many thin ones: 0.75 against 0.87 ms at 4 x 2048 tokens, 8 heads of 128), fewer while the CTAs do not fill the SMs
+  int vt = 256 / RG;
+  while (vt > 8 && (vt / 2 >= vdim || (long long)n_segs * heads * cdiv(vdim, vt) < 100)) vt /= 2;
+  static const int vt_env = env_int("PG_LIGHTNING_VT", 0);
+  if (vt_env >= 8 && vt_env <= 256 / RG && (vt_env & (vt_env - 1)) == 0) vt = vt_env;
+  const size_t smem = sizeof(float) * 2 * CH * (2 * DMAX + vt);
+  // An ordinary launch, not a programmatic dependent one: CTAs that become resident while the preceding kernel still
+  // fills the machine are placed on the few SMs with room, and a recurrence of a few hundred long-lived CTAs then runs
+  // on a fraction of the GPU (measured at 4 x 2048 tokens, 8 heads of 128: 2.06 ms against 0.88 ms).
+  lightning_kernel<DMAX, RG, CH><<<dim3(n_segs, heads, cdiv(vdim, vt)), dim3(vt * RG), smem, st>>>(
+      out, state, rec, decay, segs, heads, dim, vdim, dp, vp);
+  return check_launch("lightning");
 }
 
 template <int DMAX, int CH>
@@ -439,18 +467,32 @@ extern "C" int pg_headnorm_gate(void* out, int ld_out, const float* o, const voi
   return PG_OK;
 }
 
-extern "C" int pg_lightning_attention(float* out, float* state, const void* proj, int ld, int q_col0, int k_col0,
-                                      int v_col0, const float* decay, const int32_t* segs, int n_segs, int heads,
-                                      int dim, int vdim, int dtype, void* stream) {
-  if (n_segs <= 0) return PG_OK;
-  PG_REQUIRE(out && state && proj && decay && segs, "lightning_attention: bad arguments");
-  PG_REQUIRE(dim > 0 && dim <= 256 && vdim > 0, "lightning_attention: key size %d (1..256), value size %d", dim, vdim);
-  cudaStream_t st = (cudaStream_t)stream;
+extern "C" long long pg_lightning_record_floats(int n_tokens, int heads, int dim, int vdim) {
+  return (long long)n_tokens * heads * (2 * ((dim + 3) / 4 * 4) + (vdim + 3) / 4 * 4);
+}
+
+extern "C" int pg_lightning_prep(float* rec, const void* proj, int ld, int q_col0, int k_col0, int v_col0, int n_tokens,
+                                 int heads, int dim, int vdim, int dtype, void* stream) {
+  if (n_tokens <= 0) return PG_OK;
+  PG_REQUIRE(rec && proj && heads > 0 && dim > 0 && vdim > 0, "lightning_prep: bad arguments");
+  const int dp = (dim + 3) / 4 * 4, vp = (vdim + 3) / 4 * 4;
   PG_DISPATCH_DTYPE(dtype, T, {
-    if (dim <= 32) return launch_lightning<T, 32>(out, state, proj, ld, q_col0, k_col0, v_col0, decay, segs, n_segs, heads, dim, vdim, st);
-    if (dim <= 64) return launch_lightning<T, 64>(out, state, proj, ld, q_col0, k_col0, v_col0, decay, segs, n_segs, heads, dim, vdim, st);
-    if (dim <= 128) return launch_lightning<T, 128>(out, state, proj, ld, q_col0, k_col0, v_col0, decay, segs, n_segs, heads, dim, vdim, st);
-    return launch_lightning<T, 256>(out, state, proj, ld, q_col0, k_col0, v_col0, decay, segs, n_segs, heads, dim, vdim, st);
+    return launch_pdl("lightning_prep", lightning_prep_kernel<T>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, rec,
+                      (const T*)proj, ld, q_col0, k_col0, v_col0, (long long)n_tokens, heads, dim, vdim, dp, vp);
   });
   return PG_OK;
+}
+
+extern "C" int pg_lightning_attention(float* out, float* state, const float* rec, const float* decay, const int32_t* segs,
+                                      int n_segs, int heads, int dim, int vdim, void* stream) {
+  if (n_segs <= 0) return PG_OK;
+  PG_REQUIRE(out && state && rec && decay && segs, "lightning_attention: bad arguments");
+  PG_REQUIRE(dim > 0 && dim <= 256 && vdim > 0, "lightning_attention: key size %d (1..256), value size %d", dim, vdim);
+  cudaStream_t st = (cudaStream_t)stream;
+  // lanes per value column: a thread keeps DMAX / RG state elements, and a token is that many fused multiply-adds
+  // twice plus log2(RG) shuffle steps on the critical path of the recurrence
+  if (dim <= 32) return launch_lightning<32, 4, 16>(out, state, rec, decay, segs, n_segs, heads, dim, vdim, st);
+  if (dim <= 64) return launch_lightning<64, 8, 8>(out, state, rec, decay, segs, n_segs, heads, dim, vdim, st);
+  if (dim <= 128) return launch_lightning<128, 8, 8>(out, state, rec, decay, segs, n_segs, heads, dim, vdim, st);
+  return launch_lightning<256, 16, 4>(out, state, rec, decay, segs, n_segs, heads, dim, vdim, st);
 }

@@ -96,7 +96,11 @@ SIGNATURES = {
     "pg_moe_route_grouped": [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "pg_moe_combine_out": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "pg_glu_clamped": [_vp, _vp, _i, _i, _f, _f, _i, _vp],
-    "pg_lightning_attention": [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "pg_lightning_record_floats": [_i, _i, _i, _i],
+    "pg_lightning_prep": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "pg_lightning_attention": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pg_head_gather": [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "pg_head_scatter": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "pg_latent_prep": [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _f, _f, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _vp],
     "pg_rotary_cols": [_vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _i, _i, _vp],
     "pg_head_gemm": [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
@@ -107,7 +111,7 @@ SIGNATURES = {
                                     _i, _i, _f, _i, _i, _vp, _i, _vp, _vp, _f, _vp, _i, _vp],
 }
 _RESTYPE = {"pg_last_error": C.c_char_p, "pg_launch_count": _ull, "pg_decode_attention_ws_floats": _ll,
-            "pg_delta_record_floats": _ll}
+            "pg_delta_record_floats": _ll, "pg_lightning_record_floats": _ll}
 
 _lib = None
 

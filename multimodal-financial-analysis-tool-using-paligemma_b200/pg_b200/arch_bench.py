@@ -628,7 +628,8 @@ def birizen_work(s: dict, cfg: dict, T1: int, seqs: int) -> Dict[str, tuple]:
             nk, nv = H * dim, H * vdim
             npj = 2 * nk + 2 * nv
             add("proj", 2 * T * D * npj, 2 * (T * D + npj * D + T * npj))
-            add("lightning", 4 * T * H * dim * vdim, T * (2 * (2 * nk + nv) + 4 * nv))        # fp32 FMAs, not tensor work
+            add("lightning_prep", 0, T * (2 * nk + nv) * (2 + 4))                               # fp32 records out
+            add("lightning", 4 * T * H * dim * vdim, T * (4 * (2 * nk + nv) + 4 * nv))          # fp32 FMAs, not tensor work
             add("headnorm_gate", 0, T * nv * (4 + 2 + 2))
             add("o", 2 * T * nv * D, 2 * (T * nv + nv * D + T * D))
         else:
@@ -670,12 +671,12 @@ def _birizen_decode_bytes(s: dict, cfg: dict, B: int) -> float:
 
 
 # (Birizen op, the like op) against the MoE Mubasun and against Ninisun at equal width
-BIRIZEN_LIKE_MUBASUN = [("proj", "proj"), ("loop_in", "proj"), ("q_up", "proj"), ("q_absorb", "proj"), ("v_up_gate", "o"),
+BIRIZEN_LIKE_MUBASUN = [("proj", "proj"), ("loop_in", "o"), ("q_up", "proj"), ("q_absorb", "proj"), ("v_up_gate", "o"),
                         ("o", "o"), ("latent_prep", "qknorm_append"), ("latent_attention", "attention"),
                         ("moe_route", "moe_route"), ("moe_gather", "moe_gather"), ("moe_gate_up", "moe_gate_up"),
                         ("moe_down", "moe_down"), ("shared_gate_up", "shared_gate_up"), ("shared_down", "shared_down"),
                         ("moe_combine", "moe_combine"), ("norm", "norm"), ("head", "head")]
-BIRIZEN_LIKE_NINISUN = [("lightning", "delta_rule"), ("headnorm_gate", "headnorm_gate"), ("post_norm", "post_norm")]
+BIRIZEN_LIKE_NINISUN = [("lightning", "delta_rule"), ("lightning_prep", "delta_prep"), ("headnorm_gate", "headnorm_gate"), ("post_norm", "post_norm")]
 
 
 @torch.no_grad()

@@ -179,6 +179,8 @@ class BirizenEngine(RaggedEngine):
         self.strict = bool(strict)      # True: tensors the config does not call for raise instead of being reported
         self._init_common(device=device, dtype=dtype, page_size=page_size, gemm_impl=gemm_impl)
         self.runs = self.cfg.runs()
+        self.head_tc_min_rows = 64      # rows from which the per-head products of latent attention run grouped on tensor cores
+        self._head_maps: Dict[tuple, tuple] = {}
         self.needs_segments = any(self.cfg.layers[r.layer].kind == "lightning" for r in self.runs)
         self._repack(weights)
         for w, lc in zip(self.layers, self.cfg.layers):     # prompt portions of latent layers whose sizes the tensor-core kernel takes
@@ -293,16 +295,48 @@ class BirizenEngine(RaggedEngine):
             proj = self._linear(h, w["proj"])
         nv = a.heads * a.vdim
         o = self._new(T, nv, dtype=torch.float32)
+        rec = self._new(int(L.pg_lightning_record_floats(T, a.heads, a.dim, a.vdim)), dtype=torch.float32)
+        with tm("lightning_prep"):
+            cabi.check(L.pg_lightning_prep(ptr(rec), ptr(proj), proj.stride(0), at["q"], at["k"], at["v"], T, a.heads, a.dim,
+                                           a.vdim, self.dt, st), "lightning_prep")
         with tm("lightning"):
-            cabi.check(L.pg_lightning_attention(ptr(o), ptr(kv.state.layers[ri]), ptr(proj), proj.stride(0), at["q"], at["k"],
-                                                at["v"], ptr(w["decay"]), ptr(inp.segs), inp.n_segs, a.heads, a.dim, a.vdim,
-                                                self.dt, st), "lightning_attention")
+            cabi.check(L.pg_lightning_attention(ptr(o), ptr(kv.state.layers[ri]), ptr(rec), ptr(w["decay"]), ptr(inp.segs),
+                                                inp.n_segs, a.heads, a.dim, a.vdim, st), "lightning_attention")
         att = self._new(T, nv)
         with tm("headnorm_gate"):       # one RMS over all heads of the token: a single "head" of heads * vdim columns
             cabi.check(L.pg_headnorm_gate(ptr(att), nv, ptr(o), ptr(w["onorm"]), ptr(proj[:, at["g"]:]), proj.stride(0), T, 1,
                                           nv, self.cfg.eps, 1.0, self.dt, st), "headnorm_gate")
         with tm("o"):
             return self._linear(att, w["o"])
+
+    def _per_head(self, out, o_hs: int, a, a_hs: int, w, gate, heads: int, N: int, K: int) -> None:
+        """out[t, h * o_hs + n] = sum_k a[t, h * a_hs + k] w[h, n, k] (* sigmoid(gate[t, h * N + n])) for every head.
+        Prompt-sized 16-bit steps: the rows are regrouped by head and all heads run as ONE grouped tensor-core GEMM (the
+        experts' kernel with the heads as groups), then go back to their tokens' rows; a handful of rows, fp32 and
+        sizes the tensor-core kernel does not take: the per-head kernels of the latent-attention file."""
+        L, st, T = cabi.lib(), cabi.stream(), a.shape[0]
+        if (self.dtype != torch.float32 and T >= self.head_tc_min_rows and N % 8 == 0 and K % 8 == 0 and a_hs % 8 == 0
+                and a.stride(0) % 8 == 0 and T * heads * max(N, K) < (1 << 31)):
+            offs = self._head_offsets(T, heads)
+            ah = self._new(heads * T, K)
+            cabi.check(L.pg_head_gather(ptr(ah), ptr(a), a.stride(0), a_hs, T, heads, K, self.dt, st), "head_gather")
+            oh = self._new(heads * T, N)
+            cabi.check(L.pg_moe_gemm_act(ptr(oh), N, ptr(ah), K, None, ptr(w), ptr(offs), heads * T, heads, N, K, cabi.GLU_NONE,
+                                         0.0, 2, ptr(self.err_flag), self.dt, st), "moe_gemm (per head)")
+            cabi.check(L.pg_head_scatter(ptr(out), out.stride(0), o_hs, ptr(oh), ptr(gate), 0 if gate is None else gate.stride(0),
+                                         T, heads, N, self.dt, st), "head_scatter")
+            return
+        cabi.check(L.pg_head_gemm(ptr(out), out.stride(0), o_hs, ptr(a), a.stride(0), a_hs, ptr(w), ptr(gate),
+                                  0 if gate is None else gate.stride(0), T, heads, N, K, self.dt, st), "head_gemm")
+
+    def _head_offsets(self, T: int, heads: int) -> torch.Tensor:
+        """Group offsets of [heads, T] rows grouped by head: group h holds rows [h T, (h + 1) T)."""
+        ent = self._head_maps.get((T, heads))
+        if ent is None:
+            if len(self._head_maps) > 32:
+                self._head_maps.clear()
+            ent = self._head_maps[(T, heads)] = (torch.arange(heads + 1, dtype=torch.int32, device=self.device) * T).contiguous()
+        return ent
 
     def _latent(self, kv, inp: StepInputs, ri: int, a: LatentCfg, w: dict, h) -> torch.Tensor:
         L, st, tm, T, at = cabi.lib(), cabi.stream(), self._tm, inp.T, w["at"]
@@ -320,8 +354,7 @@ class BirizenEngine(RaggedEngine):
         hd, ld_q = a.dim + a.rot_dim, a.kv_rank + a.rot_dim
         qa = self._new(T, a.heads * ld_q)
         with tm("q_absorb"):
-            cabi.check(L.pg_head_gemm(ptr(qa), qa.stride(0), ld_q, ptr(q), q.stride(0), hd, ptr(w["uk_t"]), None, 0, T,
-                                      a.heads, a.kv_rank, a.dim, self.dt, st), "head_gemm (query absorption)")
+            self._per_head(qa, ld_q, q, hd, w["uk_t"], None, a.heads, a.kv_rank, a.dim)
             cabi.check(L.pg_rotary_cols(ptr(qa), qa.stride(0), a.kv_rank, ld_q, ptr(q), q.stride(0), a.dim, hd, a.heads,
                                         a.rot_dim, ptr(w["freq"]), w["mag"], ptr(inp.pos), T, self.dt, st), "rotary_cols")
         ol = self._new(T, a.heads * a.kv_rank)
@@ -340,9 +373,7 @@ class BirizenEngine(RaggedEngine):
                     self.attn_ws.numel(), self.dt, st), "attention_ragged_sink")
         att = self._new(T, a.heads * a.vdim)
         with tm("v_up_gate"):
-            cabi.check(L.pg_head_gemm(ptr(att), att.stride(0), a.vdim, ptr(ol), ol.stride(0), a.kv_rank, ptr(w["uv"]),
-                                      ptr(proj[:, at["g"]:]), proj.stride(0), T, a.heads, a.vdim, a.kv_rank, self.dt, st),
-                       "head_gemm (value expansion)")
+            self._per_head(att, a.vdim, ol, a.kv_rank, w["uv"], proj[:, at["g"]:], a.heads, a.vdim, a.kv_rank)
         with tm("o"):
             return self._linear(att, w["o"])
 

@@ -51,8 +51,10 @@ def test_lightning_recurrence_over_segments_and_slots(H, dim, vdim, dtype):
         row += n
     segs += [1, 0, 0]                                   # an empty segment (padding of a captured launch) touches nothing
     projd, dec = proj.cuda(), decay.cuda()
-    cabi.check(L.pg_lightning_attention(out.data_ptr(), state.data_ptr(), projd.data_ptr(), ld, 8, 8 + nk, 8 + 2 * nk,
-                                        dec.data_ptr(), _i32(segs).data_ptr(), 4, H, dim, vdim, CT[dtype], st))
+    rec = torch.empty(L.pg_lightning_record_floats(T, H, dim, vdim), device="cuda")
+    cabi.check(L.pg_lightning_prep(rec.data_ptr(), projd.data_ptr(), ld, 8, 8 + nk, 8 + 2 * nk, T, H, dim, vdim, CT[dtype], st))
+    cabi.check(L.pg_lightning_attention(out.data_ptr(), state.data_ptr(), rec.data_ptr(), dec.data_ptr(), _i32(segs).data_ptr(),
+                                        4, H, dim, vdim, st))
     p64, row = proj.to(F64), 0
     for n, s in zip(lens, slots):
         sl = slice(row, row + n)
@@ -88,9 +90,11 @@ def test_lightning_state_carries_a_first_token_far():
         state = torch.zeros(1, H, dim, vdim, device="cuda")
         out = torch.zeros(T, nv, device="cuda")
         at = 0
+        rec = torch.empty(L.pg_lightning_record_floats(T, H, dim, vdim), device="cuda")
         for n in cuts:
-            cabi.check(L.pg_lightning_attention(out[at:].data_ptr(), state.data_ptr(), projd[at:].data_ptr(), proj.shape[1], 0, nk,
-                                                2 * nk, decay.data_ptr(), _i32([0, 0, n]).data_ptr(), 1, H, dim, vdim, 0, st))
+            cabi.check(L.pg_lightning_prep(rec.data_ptr(), projd[at:].data_ptr(), proj.shape[1], 0, nk, 2 * nk, n, H, dim, vdim, 0, st))
+            cabi.check(L.pg_lightning_attention(out[at:].data_ptr(), state.data_ptr(), rec.data_ptr(), decay.data_ptr(),
+                                                _i32([0, 0, n]).data_ptr(), 1, H, dim, vdim, st))
             at += n
         _close(out, want_o.reshape(T, nv), 1e-5)
 
@@ -171,6 +175,31 @@ def test_per_head_product_with_gate(M, H, N, K, gated, dtype):
     if gated:
         want = want * O.sigmoid(gate.to(F64)[:, :H * N].view(M, H, N))
     _close(out.view(M, H, o_hs)[..., :N], want, 2e-6 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,H,K,N", [(70, 3, 16, 24), (5, 2, 7, 3), (200, 8, 128, 64)])
+def test_rows_regrouped_by_head_and_back(dtype, M, H, K, N):
+    """Token rows -> rows grouped by head (the operand layout of the grouped GEMM with heads as groups) and the
+    product's rows back into token rows with the output gate."""
+    cabi, L, st = _lib()
+    g = torch.Generator().manual_seed(31)
+    a_hs, o_hs = K + 8, N + 8
+    a = torch.randn(M, H * a_hs, generator=g).to(dtype).cuda()
+    grouped = torch.zeros(H * M, K, dtype=dtype, device="cuda")
+    cabi.check(L.pg_head_gather(grouped.data_ptr(), a.data_ptr(), H * a_hs, a_hs, M, H, K, CT[dtype], st))
+    assert torch.equal(grouped.view(H, M, K), a.view(M, H, a_hs)[..., :K].transpose(0, 1))
+    prod = torch.randn(H * M, N, generator=g).to(dtype).cuda()
+    gate = torch.randn(M, H * N + 8, generator=g).to(dtype).cuda()
+    for gated in (False, True):
+        out = torch.zeros(M, H * o_hs, dtype=dtype, device="cuda")
+        cabi.check(L.pg_head_scatter(out.data_ptr(), H * o_hs, o_hs, prod.data_ptr(), gate.data_ptr() if gated else None,
+                                     H * N + 8, M, H, N, CT[dtype], st))
+        want = prod.view(H, M, N).transpose(0, 1).cpu().to(F64)
+        if gated:
+            want = want * O.sigmoid(gate[:, :H * N].view(M, H, N).cpu().to(F64))
+        _close(out.view(M, H, o_hs)[..., :N], want, 1e-6 if dtype == torch.float32 else 6e-3)
+        assert float(out.view(M, H, o_hs)[..., N:].abs().max()) == 0
 
 
 def _latent_attention_case(H, kvr, rot, lens, new, dtype=torch.float32, tower=None, sink_value=None, seed=0):
