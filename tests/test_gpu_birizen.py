@@ -241,7 +241,8 @@ def _latent_attention_case(H, kvr, rot, lens, new, dtype=torch.float32, tower=No
     return out, torch.cat(want)
 
 
-@pytest.mark.parametrize("H,kvr,rot", [(4, 32, 8), (3, 14, 4), (2, 96, 32), (8, 64, 16), (1, 260, 4), (6, 40, 0)])
+@pytest.mark.parametrize("H,kvr,rot", [(4, 32, 8), (3, 14, 4), (2, 96, 32), (8, 64, 16), (1, 260, 4), (6, 40, 0), (16, 256, 64),
+                                       (4, 512, 64), (12, 128, 32)])
 @pytest.mark.parametrize("new", [[1, 1, 1], [40, 3, 150]])     # decoded tokens (key slices), prompt portions
 def test_latent_space_attention_with_sink(H, kvr, rot, new):
     got, want = _latent_attention_case(H, kvr, rot, [300, 70, 150], new)
