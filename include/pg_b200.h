@@ -456,12 +456,12 @@ int pg_rotary_cols(void* dst, int ld_dst, int dst_col0, int dst_head_stride, con
                    int n_tokens, int dtype, void* stream);
 int pg_head_gemm(void* out, int ldo, int out_head_stride, const void* A, int lda, int a_head_stride, const void* W,
                  const void* gate, int ld_gate, int n_rows, int heads, int N, int K, int dtype, void* stream);
-/* out[t, h*out_head_stride + n] = in[(h*n_rows + t)*N + n] (* sigmoid(gate[t, h*N + n])): rows grouped by head
- * (pg_moe_gemm with the heads as groups) back into token rows. */
-int pg_head_gather(void* out, const void* in, int ld_in, int in_head_stride, int n_rows, int heads, int K, int dtype,
-                   void* stream);   /* out[(h*n_rows + t)*K + k] = in[t*ld_in + h*in_head_stride + k] */
-int pg_head_scatter(void* out, int ldo, int out_head_stride, const void* in, const void* gate, int ld_gate, int n_rows,
-                    int heads, int N, int dtype, void* stream);
+/* pg_head_gemm_ex: impl 0 = the grouped tcgen05 kernel in its per-head mode for 16-bit row counts from 64 on (every
+ * stride and size a multiple of 8; its waits are bounded, *err_flag becomes 2 if one gives up), else the fp32-FMA
+ * kernels; 1 = the fp32-FMA kernels (pg_head_gemm); 2 = the tensor-core kernel or an error. */
+int pg_head_gemm_ex(void* out, int ldo, int out_head_stride, const void* A, int lda, int a_head_stride, const void* W,
+                    const void* gate, int ld_gate, int n_rows, int heads, int N, int K, int impl, int* err_flag, int dtype,
+                    void* stream);
 int pg_attention_ragged_sink(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
                              int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
                              const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,

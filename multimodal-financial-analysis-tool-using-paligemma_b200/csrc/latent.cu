@@ -13,8 +13,8 @@
 //   head_gemm_kernel     (64x64 tiles)    out[t, h] = A[t, h] W_h^T for every head h at once (fp32 accumulation), with an
 //                                         optional sigmoid gate on the output: the absorption of W_uk into the queries
 //                                         and the value expansion W_uv of the attended latents
-//   head_gather / head_scatter_kernel     token rows <-> rows grouped by head (the grouped tensor-core GEMM's layout), the
-//                                         way back with the same optional gate
+//                                         (prompt-sized 16-bit steps: the grouped tcgen05 GEMM of the experts in its
+//                                         per-head mode, moe_gemm_tcgen05.cu)
 //   concat_cast_kernel                    [a | b] of two fp32 matrices as one model-dtype operand row
 #include "common.cuh"
 
@@ -198,49 +198,24 @@ head_gemv_kernel(T* __restrict__ out, int ldo, int o_hs, const T* __restrict__ A
   }
 }
 
-// Regrouping between token rows [M, heads, .] and rows grouped by head [heads, M, .] (the layout the grouped tensor-core
-// GEMM takes with the heads as its groups), 16 bytes per thread and access when the sizes allow:
-//   head_gather_kernel   out[(h M + t) K + k] = in[t ld_in + h in_hs + k]
-//   head_scatter_kernel  out[t ldo + h o_hs + n] = in[(h M + t) N + n] (* sigmoid(gate[t ldg + h N + n]))
-template <typename T, int V>
-__global__ void head_gather_kernel(T* __restrict__ out, const T* __restrict__ in, int ld_in, int in_hs, unsigned M,
-                                   unsigned heads, unsigned K) {
+// out[m, h * o_hs + n] *= sigmoid(gate[m, h * N + n]), eight columns per thread: the gate of a per-head product that ran
+// on the tensor cores (whose epilogue owns a row per thread and would read the gate 16 bytes at a time across 32 rows)
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ out, int ldo, int o_hs, const T* __restrict__ gate, int ldg, unsigned M,
+                                 unsigned heads, unsigned N) {
   pdl_launch_dependents();
   pdl_wait();
-  const unsigned kp = K / V, total = M * heads * kp;
-  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const unsigned k = (i % kp) * V, r = i / kp, t = r % M, h = r / M;
-    const T* src = in + (size_t)t * ld_in + (size_t)h * in_hs + k;
-    T* dst = out + (size_t)r * K + k;
-    if constexpr (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-    else *dst = *src;
-  }
-}
-
-template <typename T, int V>
-__global__ void head_scatter_kernel(T* __restrict__ out, int ldo, int o_hs, const T* __restrict__ in,
-                                    const T* __restrict__ gate, int ldg, unsigned M, unsigned heads, unsigned N) {
-  pdl_launch_dependents();
-  pdl_wait();
+  constexpr int V = Vec<T>::N;
   const unsigned np = N / V, total = M * heads * np;
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const unsigned n = (i % np) * V, r = i / np, h = r % heads, t = r / heads;
-    const T* src = in + ((size_t)h * M + t) * N + n;
-    T* dst = out + (size_t)t * ldo + (size_t)h * o_hs + n;
+    T* o = out + (size_t)t * ldo + (size_t)h * o_hs + n;
     float f[V], g[V];
-    if constexpr (V * sizeof(T) == 16) {
-      unpack<T>(*reinterpret_cast<const uint4*>(src), f);
-      if (gate) {
-        unpack<T>(*reinterpret_cast<const uint4*>(gate + (size_t)t * ldg + h * N + n), g);
+    unpack<T>(*reinterpret_cast<const uint4*>(o), f);
+    unpack<T>(*reinterpret_cast<const uint4*>(gate + (size_t)t * ldg + h * N + n), g);
 #pragma unroll
-        for (int j = 0; j < V; ++j) f[j] = rnd<T>(f[j]) * (1.f / (1.f + __expf(-g[j])));
-      }
-      *reinterpret_cast<uint4*>(dst) = pack<T>(f);
-    } else {
-      float v = to_f<T>(*src);
-      if (gate) v *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * ldg + h * N + n])));
-      *dst = from_f<T>(v);
-    }
+    for (int j = 0; j < V; ++j) f[j] *= 1.f / (1.f + __expf(-g[j]));
+    *reinterpret_cast<uint4*>(o) = pack<T>(f);
   }
 }
 
@@ -257,6 +232,10 @@ __global__ void concat_cast_kernel(T* __restrict__ out, const float* __restrict_
     out[i] = from_f<T>(c < D ? a[r * D + c] : b[r * D + c - D]);
   }
 }
+
+bool head_gemm_tc_supported(int ldo, int o_gs, int lda, int a_gs, int N, int K, int dtype);
+int head_gemm_tc(void* out, int ldo, int o_gs, const void* A, int lda, int a_gs, const void* W, int n_rows, int heads, int N,
+                 int K, int dtype, int* err_flag, cudaStream_t st);
 
 }  // namespace pg
 
@@ -298,12 +277,30 @@ extern "C" int pg_rotary_cols(void* dst, int ld_dst, int dst_col0, int dst_head_
   return PG_OK;
 }
 
-extern "C" int pg_head_gemm(void* out, int ldo, int out_head_stride, const void* A, int lda, int a_head_stride,
-                            const void* W, const void* gate, int ld_gate, int n_rows, int heads, int N, int K, int dtype,
-                            void* stream) {
+extern "C" int pg_head_gemm_ex(void* out, int ldo, int out_head_stride, const void* A, int lda, int a_head_stride,
+                               const void* W, const void* gate, int ld_gate, int n_rows, int heads, int N, int K, int impl,
+                               int* err_flag, int dtype, void* stream) {
   if (n_rows <= 0) return PG_OK;
   PG_REQUIRE(out && A && W && heads > 0 && N > 0 && K > 0, "head_gemm: bad arguments");
   cudaStream_t st = (cudaStream_t)stream;
+  // impl 0: prompt-sized 16-bit row counts on the tensor cores (all heads in one launch of the grouped kernel) where the
+  // sizes allow; 1: the fp32-FMA kernels; 2: the tensor-core kernel or an error
+  static const int tc_min_rows = env_int("PG_HEAD_GEMM_TC_MIN_ROWS", 64);
+  const bool tc_ok = head_gemm_tc_supported(ldo, out_head_stride, lda, a_head_stride, N, K, dtype) &&
+                     (long long)lda >= (long long)(heads - 1) * a_head_stride + K && (!gate || ld_gate % 8 == 0) &&
+                     ((uintptr_t)gate % 16) == 0 && (long long)n_rows * heads * N < (1ll << 31);
+  PG_REQUIRE(impl != 2 || tc_ok, "head_gemm: the tensor-core kernel does not take this problem (N=%d K=%d dtype %d)", N, K, dtype);
+  if (impl == 2 || (impl == 0 && tc_ok && n_rows >= tc_min_rows)) {
+    const int rc = head_gemm_tc(out, ldo, out_head_stride, A, lda, a_head_stride, W, n_rows, heads, N, K, dtype, err_flag, st);
+    if (rc != PG_OK || !gate) return rc;
+    const long long total = (long long)n_rows * heads * (N / 8);
+    const int blocks = (int)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+    if (dtype == PG_BF16)
+      return launch_pdl("head_gate", head_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, st, (bf16*)out, ldo, out_head_stride,
+                        (const bf16*)gate, ld_gate, (unsigned)n_rows, (unsigned)heads, (unsigned)N);
+    return launch_pdl("head_gate", head_gate_kernel<f16>, dim3(blocks), dim3(256), 0, st, (f16*)out, ldo, out_head_stride,
+                      (const f16*)gate, ld_gate, (unsigned)n_rows, (unsigned)heads, (unsigned)N);
+  }
   PG_DISPATCH_DTYPE(dtype, T, {
     if (n_rows <= 2 * HV_ROWS && (size_t)HV_ROWS * K * sizeof(float) <= 96 * 1024) {
       const int warps = 8;
@@ -320,41 +317,11 @@ extern "C" int pg_head_gemm(void* out, int ldo, int out_head_stride, const void*
   return PG_OK;
 }
 
-extern "C" int pg_head_gather(void* out, const void* in, int ld_in, int in_head_stride, int n_rows, int heads, int K,
-                              int dtype, void* stream) {
-  if (n_rows <= 0) return PG_OK;
-  PG_REQUIRE(out && in && heads > 0 && K > 0 && (long long)n_rows * heads * K < (1ll << 31), "head_gather: bad arguments");
-  PG_DISPATCH_DTYPE(dtype, T, {
-    constexpr int V = Vec<T>::N;
-    const bool vec = K % V == 0 && ld_in % V == 0 && in_head_stride % V == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)in % 16) == 0;
-    const long long total = (long long)n_rows * heads * (vec ? K / V : K);
-    const int blocks = (int)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
-    if (vec)
-      return launch_pdl("head_gather", head_gather_kernel<T, V>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
-                        (const T*)in, ld_in, in_head_stride, (unsigned)n_rows, (unsigned)heads, (unsigned)K);
-    return launch_pdl("head_gather", head_gather_kernel<T, 1>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
-                      (const T*)in, ld_in, in_head_stride, (unsigned)n_rows, (unsigned)heads, (unsigned)K);
-  });
-  return PG_OK;
-}
-
-extern "C" int pg_head_scatter(void* out, int ldo, int out_head_stride, const void* in, const void* gate, int ld_gate,
-                               int n_rows, int heads, int N, int dtype, void* stream) {
-  if (n_rows <= 0) return PG_OK;
-  PG_REQUIRE(out && in && heads > 0 && N > 0 && (long long)n_rows * heads * N < (1ll << 31), "head_scatter: bad arguments");
-  PG_DISPATCH_DTYPE(dtype, T, {
-    constexpr int V = Vec<T>::N;
-    const bool vec = N % V == 0 && ldo % V == 0 && out_head_stride % V == 0 && (!gate || ld_gate % V == 0) &&
-                     ((uintptr_t)out % 16) == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)gate % 16) == 0;
-    const long long total = (long long)n_rows * heads * (vec ? N / V : N);
-    const int blocks = (int)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
-    if (vec)
-      return launch_pdl("head_scatter", head_scatter_kernel<T, V>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
-                        ldo, out_head_stride, (const T*)in, (const T*)gate, ld_gate, (unsigned)n_rows, (unsigned)heads, (unsigned)N);
-    return launch_pdl("head_scatter", head_scatter_kernel<T, 1>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out,
-                      ldo, out_head_stride, (const T*)in, (const T*)gate, ld_gate, (unsigned)n_rows, (unsigned)heads, (unsigned)N);
-  });
-  return PG_OK;
+extern "C" int pg_head_gemm(void* out, int ldo, int out_head_stride, const void* A, int lda, int a_head_stride,
+                            const void* W, const void* gate, int ld_gate, int n_rows, int heads, int N, int K, int dtype,
+                            void* stream) {
+  return pg_head_gemm_ex(out, ldo, out_head_stride, A, lda, a_head_stride, W, gate, ld_gate, n_rows, heads, N, K, 1, nullptr,
+                         dtype, stream);
 }
 
 extern "C" int pg_concat_cast(void* out, const float* a, const float* b, int rows, int D, int dtype, void* stream) {

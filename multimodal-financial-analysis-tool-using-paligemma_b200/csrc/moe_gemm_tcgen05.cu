@@ -26,6 +26,10 @@ struct MoeParams {
   int* err_flag;   // device-visible int, set to 2 when a pipeline wait gave up (may be NULL)
   int act;         // pairing of the two products of a stacked [Wg; Wu] tile: PG_GLU_SILU or PG_GLU_CLAMPED
   float limit;     // PG_GLU_CLAMPED: g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1)
+  // Per-head mode (group_rows > 0; offsets unused): every group is one head of the SAME group_rows token rows.  Group e
+  // reads its operand at columns e * a_gs of the token rows (the A map covers the token-major matrix) and writes
+  // columns e * o_gs of them.
+  int group_rows, a_gs, o_gs;
 };
 
 // Every wait of this kernel is bounded: if the roles ever disagreed about the tile sequence (the offsets are data),
@@ -46,19 +50,22 @@ __device__ __forceinline__ bool mbar_wait_lim(uint32_t bar, uint32_t parity, vol
 struct TileCursor {
   const int32_t* off;
   int n_experts, n_tiles_n, e, first;   // first = number of the first tile of expert e
-  __device__ __forceinline__ TileCursor(const int32_t* o, int ne, int ntn) : off(o), n_experts(ne), n_tiles_n(ntn), e(0), first(0) {}
+  int fixed;                            // > 0: every group has this many rows (off is not read)
+  __device__ __forceinline__ TileCursor(const int32_t* o, int ne, int ntn, int fx = 0)
+      : off(o), n_experts(ne), n_tiles_n(ntn), e(0), first(0), fixed(fx) {}
+  __device__ __forceinline__ int at(int i) const { return fixed > 0 ? i * fixed : off[i]; }
   // -> false when the sequence is exhausted
   __device__ __forceinline__ bool seek(int tile, int& expert, int& m0, int& m_end, int& n_blk) {
     while (e < n_experts) {
-      const int rows = off[e + 1] - off[e];
+      const int rows = at(e + 1) - at(e);
       const int mt = (rows + MG_BM - 1) / MG_BM;
       const int cnt = mt * n_tiles_n;
       if (tile < first + cnt) {
         const int i = tile - first;
         expert = e;
         n_blk = i / mt;
-        m0 = off[e] + (i % mt) * MG_BM;
-        m_end = off[e + 1];
+        m0 = at(e) + (i % mt) * MG_BM;
+        m_end = at(e + 1);
         return true;
       }
       first += cnt;
@@ -120,7 +127,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      TileCursor cur(p.offsets, p.n_experts, n_tiles_n);
+      TileCursor cur(p.offsets, p.n_experts, n_tiles_n, p.group_rows);
       int e, m0, m_end, n_blk;
       for (int tile = blockIdx.x; cur.seek(tile, e, m0, m_end, n_blk); tile += gridDim.x) {
         const int w_row = e * rows_per_expert + n_blk * BN;
@@ -128,7 +135,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           if (!mbar_wait_lim(empty_bar(stage), phase ^ 1, fail)) goto producer_done;
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-          tma_load_2d(sa, &map_a, full_bar(stage), kb * MG_BK, m0);
+          if (p.group_rows > 0) tma_load_2d(sa, &map_a, full_bar(stage), e * p.a_gs + kb * MG_BK, m0 - e * p.group_rows);
+          else tma_load_2d(sa, &map_a, full_bar(stage), kb * MG_BK, m0);
           tma_load_2d(sa + MG_A_BYTES, &map_w, full_bar(stage), kb * MG_BK, w_row);
           if (DUAL) tma_load_2d(sa + MG_A_BYTES + W_BYTES, &map_w, full_bar(stage), kb * MG_BK, w_row + p.N);
           if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
@@ -140,7 +148,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     if (lane == 0) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      TileCursor cur(p.offsets, p.n_experts, n_tiles_n);
+      TileCursor cur(p.offsets, p.n_experts, n_tiles_n, p.group_rows);
       int e, m0, m_end, n_blk;
       for (int tile = blockIdx.x; cur.seek(tile, e, m0, m_end, n_blk); tile += gridDim.x) {
         if (!mbar_wait_lim(tempty_bar(acc), acc_phase ^ 1, fail)) goto mma_done;
@@ -170,12 +178,14 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     int acc = 0;
     uint32_t acc_phase = 0;
     T* out = reinterpret_cast<T*>(p.out);
-    TileCursor cur(p.offsets, p.n_experts, n_tiles_n);
+    TileCursor cur(p.offsets, p.n_experts, n_tiles_n, p.group_rows);
     int e, m0, m_end, n_blk;
     for (int tile = blockIdx.x; cur.seek(tile, e, m0, m_end, n_blk); tile += gridDim.x) {
       if (!mbar_wait_lim(tfull_bar(acc), acc_phase, fail)) break;
       tc_fence_after();
       const int m = m0 + q * 32 + lane;
+      // where this thread's row goes: the grouped row itself, or (per-head mode) its token row at the head's columns
+      const size_t o_at = p.group_rows > 0 ? (size_t)(m - e * p.group_rows) * p.ldo + (size_t)e * p.o_gs : (size_t)m * p.ldo;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * ACC_COLS;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -204,7 +214,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
               }
               o[j] = x;
             }
-            *reinterpret_cast<uint4*>(out + (size_t)m * p.ldo + n0 + j0) = pack<T>(o);
+            *reinterpret_cast<uint4*>(out + o_at + n0 + j0) = pack<T>(o);
           }
         }
       }
@@ -265,13 +275,38 @@ int moe_gemm_tc(void* out, int ldo, const void* A, int lda, const int32_t* row_m
   PG_REQUIRE(tc::make_map_2d(&ma, A, n_pairs, K, lda, tc::MG_BM, bf) &&
                  tc::make_map_2d(&mw, W, (long long)n_experts * rows_per_expert, K, K, bn, bf),
              "moe_gemm_tc: cuTensorMapEncodeTiled failed (rows=%d N=%d K=%d)", n_pairs, N, K);
-  tc::MoeParams p = {out, offsets, n_experts, N, K, ldo, err_flag, act, limit};
+  tc::MoeParams p = {out, offsets, n_experts, N, K, ldo, err_flag, act, limit, 0, 0, 0};
   const int max_tiles = (cdiv(n_pairs, tc::MG_BM) + n_experts) * cdiv(N, bn);
 #define PG_MOE(D, B) return bf ? tc::launch_moe<bf16, D, B>(ma, mw, p, max_tiles, st) : tc::launch_moe<f16, D, B>(ma, mw, p, max_tiles, st)
   if (swiglu) { if (bn == 128) { PG_MOE(true, 128); } PG_MOE(true, 64); }
   if (bn == 128) { PG_MOE(false, 128); }
   PG_MOE(false, 64);
 #undef PG_MOE
+}
+
+// Per-head products on token rows: out[t, h * o_gs + n] = sum_k A[t, h * a_gs + k] W[h][n][k] for all heads in ONE launch
+// of the grouped kernel (a group = a head, every group the same n_rows token rows).
+bool head_gemm_tc_supported(int ldo, int o_gs, int lda, int a_gs, int N, int K, int dtype) {
+  static const int enabled = env_int("PG_HEAD_GEMM_TC", 1);
+  if (!enabled || (dtype != PG_BF16 && dtype != PG_F16)) return false;
+  if (N % 8 || K % 8 || lda % 8 || ldo % 8 || a_gs % 8 || o_gs % 8) return false;
+  return tc::encode_fn() != nullptr;
+}
+
+int head_gemm_tc(void* out, int ldo, int o_gs, const void* A, int lda, int a_gs, const void* W, int n_rows, int heads, int N,
+                 int K, int dtype, int* err_flag, cudaStream_t st) {
+  PG_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)out % 16) == 0,
+             "head_gemm_tc: operands must be 16-byte aligned");
+  const bool bf = dtype == PG_BF16;
+  const int bn = N >= 128 ? 128 : 64;
+  CUtensorMap ma, mw;
+  PG_REQUIRE(tc::make_map_2d(&ma, A, n_rows, lda, lda, tc::MG_BM, bf) &&
+                 tc::make_map_2d(&mw, W, (long long)heads * N, K, K, bn, bf),
+             "head_gemm_tc: cuTensorMapEncodeTiled failed (rows=%d N=%d K=%d)", n_rows, N, K);
+  tc::MoeParams p = {out, nullptr, heads, N, K, ldo, err_flag, PG_GLU_NONE, 0.f, n_rows, a_gs, o_gs};
+  const int max_tiles = heads * cdiv(n_rows, tc::MG_BM) * cdiv(N, bn);
+  if (bn == 128) return bf ? tc::launch_moe<bf16, false, 128>(ma, mw, p, max_tiles, st) : tc::launch_moe<f16, false, 128>(ma, mw, p, max_tiles, st);
+  return bf ? tc::launch_moe<bf16, false, 64>(ma, mw, p, max_tiles, st) : tc::launch_moe<f16, false, 64>(ma, mw, p, max_tiles, st);
 }
 
 }  // namespace pg

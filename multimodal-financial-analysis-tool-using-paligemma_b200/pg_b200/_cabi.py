@@ -99,11 +99,10 @@ SIGNATURES = {
     "pg_lightning_record_floats": [_i, _i, _i, _i],
     "pg_lightning_prep": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "pg_lightning_attention": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
-    "pg_head_gather": [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-    "pg_head_scatter": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "pg_latent_prep": [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _f, _f, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _vp],
     "pg_rotary_cols": [_vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _i, _i, _vp],
     "pg_head_gemm": [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "pg_head_gemm_ex": [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],
     "pg_attention_ragged_sink": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i,
                                  _i, _f, _i, _i, _vp, _i, _vp, _vp, _f, _vp, _ll, _i, _vp],
     "pg_concat_cast": [_vp, _vp, _vp, _i, _i, _i, _vp],

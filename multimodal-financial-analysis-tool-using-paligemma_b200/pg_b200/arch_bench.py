@@ -671,7 +671,7 @@ def _birizen_decode_bytes(s: dict, cfg: dict, B: int) -> float:
 
 
 # (Birizen op, the like op) against the MoE Mubasun and against Ninisun at equal width
-BIRIZEN_LIKE_MUBASUN = [("proj", "proj"), ("loop_in", "o"), ("q_up", "proj"), ("q_absorb", "proj"), ("v_up_gate", "o"),
+BIRIZEN_LIKE_MUBASUN = [("proj", "proj"), ("loop_in", "o"), ("q_up", "proj"), ("q_absorb", "moe_down"), ("v_up_gate", "moe_down"),
                         ("o", "o"), ("latent_prep", "qknorm_append"), ("latent_attention", "attention"),
                         ("moe_route", "moe_route"), ("moe_gather", "moe_gather"), ("moe_gate_up", "moe_gate_up"),
                         ("moe_down", "moe_down"), ("shared_gate_up", "shared_gate_up"), ("shared_down", "shared_down"),

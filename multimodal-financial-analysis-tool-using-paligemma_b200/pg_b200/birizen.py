@@ -179,8 +179,7 @@ class BirizenEngine(RaggedEngine):
         self.strict = bool(strict)      # True: tensors the config does not call for raise instead of being reported
         self._init_common(device=device, dtype=dtype, page_size=page_size, gemm_impl=gemm_impl)
         self.runs = self.cfg.runs()
-        self.head_tc_min_rows = 64      # rows from which the per-head products of latent attention run grouped on tensor cores
-        self._head_maps: Dict[tuple, tuple] = {}
+        self.head_impl = 0              # per-head products of latent attention: 0 = tensor cores where they fit, 1 = fp32 FMA
         self.needs_segments = any(self.cfg.layers[r.layer].kind == "lightning" for r in self.runs)
         self._repack(weights)
         for w, lc in zip(self.layers, self.cfg.layers):     # prompt portions of latent layers whose sizes the tensor-core kernel takes
@@ -310,33 +309,12 @@ class BirizenEngine(RaggedEngine):
             return self._linear(att, w["o"])
 
     def _per_head(self, out, o_hs: int, a, a_hs: int, w, gate, heads: int, N: int, K: int) -> None:
-        """out[t, h * o_hs + n] = sum_k a[t, h * a_hs + k] w[h, n, k] (* sigmoid(gate[t, h * N + n])) for every head.
-        Prompt-sized 16-bit steps: the rows are regrouped by head and all heads run as ONE grouped tensor-core GEMM (the
-        experts' kernel with the heads as groups), then go back to their tokens' rows; a handful of rows, fp32 and
-        sizes the tensor-core kernel does not take: the per-head kernels of the latent-attention file."""
-        L, st, T = cabi.lib(), cabi.stream(), a.shape[0]
-        if (self.dtype != torch.float32 and T >= self.head_tc_min_rows and N % 8 == 0 and K % 8 == 0 and a_hs % 8 == 0
-                and a.stride(0) % 8 == 0 and T * heads * max(N, K) < (1 << 31)):
-            offs = self._head_offsets(T, heads)
-            ah = self._new(heads * T, K)
-            cabi.check(L.pg_head_gather(ptr(ah), ptr(a), a.stride(0), a_hs, T, heads, K, self.dt, st), "head_gather")
-            oh = self._new(heads * T, N)
-            cabi.check(L.pg_moe_gemm_act(ptr(oh), N, ptr(ah), K, None, ptr(w), ptr(offs), heads * T, heads, N, K, cabi.GLU_NONE,
-                                         0.0, 2, ptr(self.err_flag), self.dt, st), "moe_gemm (per head)")
-            cabi.check(L.pg_head_scatter(ptr(out), out.stride(0), o_hs, ptr(oh), ptr(gate), 0 if gate is None else gate.stride(0),
-                                         T, heads, N, self.dt, st), "head_scatter")
-            return
-        cabi.check(L.pg_head_gemm(ptr(out), out.stride(0), o_hs, ptr(a), a.stride(0), a_hs, ptr(w), ptr(gate),
-                                  0 if gate is None else gate.stride(0), T, heads, N, K, self.dt, st), "head_gemm")
-
-    def _head_offsets(self, T: int, heads: int) -> torch.Tensor:
-        """Group offsets of [heads, T] rows grouped by head: group h holds rows [h T, (h + 1) T)."""
-        ent = self._head_maps.get((T, heads))
-        if ent is None:
-            if len(self._head_maps) > 32:
-                self._head_maps.clear()
-            ent = self._head_maps[(T, heads)] = (torch.arange(heads + 1, dtype=torch.int32, device=self.device) * T).contiguous()
-        return ent
+        """out[t, h * o_hs + n] = sum_k a[t, h * a_hs + k] w[h, n, k] (* sigmoid(gate[t, h * N + n])) for every head:
+        prompt-sized 16-bit steps as ONE launch of the experts' grouped tensor-core GEMM with the heads as its groups,
+        a handful of rows, fp32 and sizes that kernel does not take on the per-head kernels of the latent-attention file."""
+        cabi.check(cabi.lib().pg_head_gemm_ex(ptr(out), out.stride(0), o_hs, ptr(a), a.stride(0), a_hs, ptr(w), ptr(gate),
+                                              0 if gate is None else gate.stride(0), a.shape[0], heads, N, K, self.head_impl,
+                                              ptr(self.err_flag), self.dt, cabi.stream()), "head_gemm")
 
     def _latent(self, kv, inp: StepInputs, ri: int, a: LatentCfg, w: dict, h) -> torch.Tensor:
         L, st, tm, T, at = cabi.lib(), cabi.stream(), self._tm, inp.T, w["at"]

@@ -177,29 +177,31 @@ def test_per_head_product_with_gate(M, H, N, K, gated, dtype):
     _close(out.view(M, H, o_hs)[..., :N], want, 2e-6 if dtype == torch.float32 else 1e-2)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("M,H,K,N", [(70, 3, 16, 24), (5, 2, 7, 3), (200, 8, 128, 64)])
-def test_rows_regrouped_by_head_and_back(dtype, M, H, K, N):
-    """Token rows -> rows grouped by head (the operand layout of the grouped GEMM with heads as groups) and the
-    product's rows back into token rows with the output gate."""
+@pytest.mark.parametrize("M", [64, 150, 300])
+@pytest.mark.parametrize("H,N,K,gated", [(3, 16, 24, True), (4, 96, 64, False), (8, 192, 128, False), (5, 128, 192, True),
+                                         (2, 40, 72, True)])
+def test_per_head_product_on_the_tensor_cores(M, H, N, K, gated):
+    """All heads in one launch of the grouped tcgen05 kernel: operand columns and output columns of a head inside the
+    token rows (head strides wider than the sizes used), row counts off the 128-row tile, K off the 64-column box."""
     cabi, L, st = _lib()
-    g = torch.Generator().manual_seed(31)
-    a_hs, o_hs = K + 8, N + 8
-    a = torch.randn(M, H * a_hs, generator=g).to(dtype).cuda()
-    grouped = torch.zeros(H * M, K, dtype=dtype, device="cuda")
-    cabi.check(L.pg_head_gather(grouped.data_ptr(), a.data_ptr(), H * a_hs, a_hs, M, H, K, CT[dtype], st))
-    assert torch.equal(grouped.view(H, M, K), a.view(M, H, a_hs)[..., :K].transpose(0, 1))
-    prod = torch.randn(H * M, N, generator=g).to(dtype).cuda()
-    gate = torch.randn(M, H * N + 8, generator=g).to(dtype).cuda()
-    for gated in (False, True):
-        out = torch.zeros(M, H * o_hs, dtype=dtype, device="cuda")
-        cabi.check(L.pg_head_scatter(out.data_ptr(), H * o_hs, o_hs, prod.data_ptr(), gate.data_ptr() if gated else None,
-                                     H * N + 8, M, H, N, CT[dtype], st))
-        want = prod.view(H, M, N).transpose(0, 1).cpu().to(F64)
-        if gated:
-            want = want * O.sigmoid(gate[:, :H * N].view(M, H, N).cpu().to(F64))
-        _close(out.view(M, H, o_hs)[..., :N], want, 1e-6 if dtype == torch.float32 else 6e-3)
-        assert float(out.view(M, H, o_hs)[..., N:].abs().max()) == 0
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(37)
+    a_hs, o_hs = K + 8, N + 16
+    A = torch.randn(M, H * a_hs, generator=g).to(dtype)
+    W = (torch.randn(H, N, K, generator=g) / math.sqrt(K)).to(dtype)
+    gate = torch.randn(M, H * N + 8, generator=g).to(dtype)
+    out = torch.zeros(M, H * o_hs, dtype=dtype, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dev = [t.cuda() for t in (A, W, gate)]
+    cabi.check(L.pg_head_gemm_ex(out.data_ptr(), H * o_hs, o_hs, dev[0].data_ptr(), H * a_hs, a_hs, dev[1].data_ptr(),
+                                 dev[2].data_ptr() if gated else None, H * N + 8, M, H, N, K, 2, err.data_ptr(), CT[dtype], st))
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    want = torch.einsum("mhk,hnk->mhn", A.to(F64).view(M, H, a_hs)[..., :K], W.to(F64))
+    if gated:
+        want = want * O.sigmoid(gate.to(F64)[:, :H * N].view(M, H, N))
+    _close(out.view(M, H, o_hs)[..., :N], want, 1e-2)
+    assert float(out.view(M, H, o_hs)[..., N:].abs().max()) == 0          # nothing beside a head's columns is written
 
 
 def _latent_attention_case(H, kvr, rot, lens, new, dtype=torch.float32, tower=None, sink_value=None, seed=0):
