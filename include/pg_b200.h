@@ -480,6 +480,72 @@ int pg_attention_ragged_tc_sink(void* out, int ld_out, const void* q, int ld_q, 
                                 int sigmoid_weights, const float* head_bias, const float* sink, float out_scale,
                                 int* err_flag, int dtype, void* stream);
 
+/* ---- norms stored around zero, short convolutions over time, per-head norms with rotated values, blocked masks,
+ * ---- the selective state-space mixer ------------------------------------------------------------------------------
+ * pg_group_rmsnorm_ex: pg_group_rmsnorm with two switches.  one_plus != 0: the weight is stored around zero and the
+ *   row is multiplied by 1 + w (the sum in fp32).  out_f32 != 0: out is fp32 [rows, D], not rounded (for a consumer
+ *   that goes on in fp32).
+ * pg_time_conv_residual: out[t] = in[t] + sum_j w[:, j] in_(t - taps + 1 + j) per channel, a causal convolution over
+ *   the positions of the token's sequence (w [C][taps], model dtype, last column = the current token; in fp32
+ *   [n_tokens, C]; out model dtype).  Inputs of earlier positions are the rows right before the token while they
+ *   belong to the same sequence (same tok_slot), beyond that the sequence's state [slots][taps - 1][C] fp32 (entry
+ *   taps - 2 the most recent; zeros for a new sequence).
+ * pg_time_conv_state: after the step's readers: for every segment {slot, first row, tokens} the state becomes the last
+ *   taps - 1 inputs of [old state ; rows of the segment], the rows read from src (fp32 when src_f32 != 0, else the
+ *   model dtype) at columns col0 .. col0 + C of rows with stride ld.  Segments of 0 tokens are skipped.
+ * pg_headnorm_rotary_append: per token, from one fused projection row: every query / key head is divided by its root
+ *   mean square over dim and multiplied by q_w / k_w (dim entries shared by the heads; NULL: no norm), then rotated as
+ *   in pg_rotary_append (no magnitude); every value head is divided by its root mean square over vdim when v_norm != 0
+ *   and, with v_freq (device float [vdim / 2]), rotated over all its columns by position * v_freq[m] (pairs (2m, 2m+1)
+ *   when v_interleaved != 0, else (m, m + vdim / 2)).  Queries to q_out (packed), keys and values to the paged pools.
+ * pg_attention_ragged_masked: pg_attention_ragged_sink with chunk > 0: key j is visible to the query at position i only
+ *   if j <= i and floor(i / chunk) == floor(j / chunk) (together with the window when one is given), and out_rot
+ *   (device float [vdim / 2], may be NULL): every head's result is turned back by -i * out_rot[m] in the pair layout
+ *   out_rot_interleaved names, in fp32 before the gate and the single rounding (values cached rotated by their
+ *   positions).
+ * pg_relu2: out = max(z, 0)^2 (out may alias z).
+ * pg_ssm_prep / pg_gate_groupnorm: the state-space mixer around the decayed linear-attention scan.  From the fused
+ *   projection row [z | x | B | C | dt] (x, B, C from column xbc_col0, dt from dt_col0): causal convolution (conv_w
+ *   [channels][taps], conv_b, channels = heads * vdim + 2 * groups * state; state of earlier inputs as for
+ *   pg_time_conv_residual, kept by pg_time_conv_state over the projection's columns) and silu on x, B, C;
+ *   step = softplus(dt + dt_bias[h]); one fp32 record per (token, head): [C | step * B | x | exp(-exp(a_log[h]) step),
+ *   0, 0, 0] with C, B padded to state rounded up to 4 floats and x to vdim likewise: the records of
+ *   pg_lightning_attention_ex with a decay per token.  rec holds pg_ssm_record_floats() floats.
+ *   pg_gate_groupnorm: out = RMS over each of `groups` equal parts of (y * silu(z)) times w (w may be NULL); y fp32
+ *   [n_tokens, cols] packed, z model dtype with row stride ld_z.
+ * pg_lightning_attention_ex: pg_lightning_attention with skip (device float [heads], may be NULL: skip[h] * v is added
+ *   to the output) and, when decay == NULL, records that carry [decay, 0, 0, 0] after the values: S <- decay_t S + k v^T. */
+int pg_group_rmsnorm_ex(void* out, float* x, const void* add_a, int lda, const void* add_b, int ldb, const void* w,
+                        const int32_t* rows_idx, int rows, int D, int groups, float eps, int one_plus, int out_f32,
+                        int dtype, void* stream);
+int pg_time_conv_residual(void* out, const float* in, const void* w, const float* state, const int32_t* tok_slot,
+                          int n_tokens, int C, int taps, int dtype, void* stream);
+int pg_time_conv_state(float* state, const void* src, int ld, int col0, int src_f32, const int32_t* segs, int n_segs,
+                       int C, int taps, int dtype, void* stream);
+int pg_headnorm_rotary_append(void* q_out, const void* proj, int ld, int q_col0, int n_heads, int k_col0, int n_kv_heads,
+                              int dim, int v_col0, int vdim, const void* q_w, const void* k_w, float eps,
+                              const float* freq, int rot_dims, int interleaved, int v_norm, const float* v_freq,
+                              int v_interleaved, void* k_pool, void* v_pool, const int32_t* page_table, int pt_stride,
+                              int page_size, const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens, int dtype,
+                              void* stream);
+int pg_attention_ragged_masked(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                               int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
+                               const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,
+                               const int32_t* tok_pos, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
+                               float scale, int window, int keep_first, int chunk, const float* slopes,
+                               int sigmoid_weights, const float* head_bias, const float* sink, const float* out_rot,
+                               int out_rot_interleaved, float out_scale, float* ws, long long ws_floats, int dtype,
+                               void* stream);
+int pg_relu2(void* out, const void* z, long long n, int dtype, void* stream);
+long long pg_ssm_record_floats(int n_tokens, int heads, int vdim, int state);
+int pg_ssm_prep(float* rec, const void* proj, int ld, int xbc_col0, int dt_col0, const void* conv_w, const void* conv_b,
+                const float* conv_state, const float* dt_bias, const float* a_log, const int32_t* tok_slot, int n_tokens,
+                int heads, int vdim, int state, int groups, int taps, int dtype, void* stream);
+int pg_gate_groupnorm(void* out, int ld_out, const float* y, const void* z, int ld_z, const void* w, int n_tokens, int cols,
+                      int groups, float eps, int dtype, void* stream);
+int pg_lightning_attention_ex(float* out, float* state, const float* rec, const float* decay, const float* skip,
+                              const int32_t* segs, int n_segs, int heads, int dim, int vdim, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -102,13 +102,17 @@ struct RagAttnParams {
   float out_scale;
   int ld_k, ld_v;                // elements between the rows of the key / value pool (>= G * dim, G * vdim)
   const float* sink;             // per query head: exp(sink[h]) joins the softmax denominator (no key, no value)
+  int chunk;                     // > 0: a key is visible only inside the query's block of `chunk` positions
+  const float* out_rot;          // [vdim / 2]: the result is turned back by -position * out_rot[m] (rotated values)
+  int out_rot_interleaved;       // pairs (2m, 2m + 1) instead of (m, m + vdim / 2)
 };
 
 // The visible keys of a token at position pos as one list: n_keep kept first positions, then [lo, pos].
 struct KeyRange {
   int lo, n_keep, count;
-  __device__ __forceinline__ KeyRange(int pos, int window, int keep_first) {
+  __device__ __forceinline__ KeyRange(int pos, int window, int keep_first, int chunk = 0) {
     lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);   // blocks are counted from position 0 of the sequence
     n_keep = min(max(keep_first, 0), lo);
     count = n_keep + pos - lo + 1;
   }
@@ -168,6 +172,38 @@ __device__ __forceinline__ void attend_range(const RagAttnParams& p, const float
   }
 }
 
+// The pair partner of every column a lane owns, for turning the result back by the query's position: columns
+// lane * DPL + i of the lanes of one warp.  Pairs that lie in one lane or at the same index of another lane take one
+// shuffle at most; any other width walks the lane's DPL values.
+template <int DPL>
+__device__ __forceinline__ void rotate_back(const RagAttnParams& p, int t, float* val) {
+  const int lane = threadIdx.x & 31, half = p.vdim >> 1;
+  const float fpos = (float)p.tok_pos[t];
+  float res[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int c = lane * DPL + i;
+    const bool in = c < 2 * half;
+    bool first;
+    int pair, pc;
+    if (p.out_rot_interleaved) { first = !(c & 1); pair = c >> 1; pc = c ^ 1; }
+    else { first = c < half; pair = first ? c : c - half; pc = first ? c + half : c - half; }
+    if (!in) pc = c;
+    const int src_lane = pc / DPL, src_i = pc % DPL;
+    float other = 0.f;
+#pragma unroll
+    for (int ii = 0; ii < DPL; ++ii) {
+      const float s = __shfl_sync(0xffffffffu, val[ii], src_lane);
+      if (ii == src_i) other = s;
+    }
+    float sn = 0.f, cs = 1.f;
+    if (in) sincosf(-fpos * p.out_rot[pair], &sn, &cs);
+    res[i] = in ? (first ? val[i] * cs - other * sn : val[i] * cs + other * sn) : val[i];
+  }
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) val[i] = res[i];
+}
+
 template <typename T, int DPL>
 __device__ __forceinline__ void store_out(const RagAttnParams& p, int t, int h, float m, float l, const float* acc) {
   const int lane = threadIdx.x & 31;
@@ -177,11 +213,15 @@ __device__ __forceinline__ void store_out(const RagAttnParams& p, int t, int h, 
   float inv = (p.sigmoid_weights ? 1.f : 1.f / l) * p.out_scale;
   if (p.gate && p.gate_per_head)
     inv *= 1.f / (1.f + expf(-to_f<T>(reinterpret_cast<const T*>(p.gate)[(size_t)t * p.ld_gate + h])));
+  float val[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) val[i] = acc[i] * inv;
+  if (p.out_rot) rotate_back<DPL>(p, t, val);                      // before the gate: the gate is per column
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
     const int c = lane * DPL + i;
     if (c < p.vdim) {
-      float v = acc[i] * inv;
+      float v = val[i];
       if (gt) v *= 1.f / (1.f + expf(-to_f<T>(gt[c])));
       o[c] = from_f<T>(v);
     }
@@ -203,7 +243,7 @@ __global__ void __launch_bounds__(256) attention_ragged_kernel(RagAttnParams p) 
   __syncwarp();
   const int pos = p.tok_pos[t];
   const int32_t* pt_row = p.page_table + (size_t)p.tok_slot[t] * p.pt_stride;
-  const KeyRange kr(pos, p.window, p.keep_first);
+  const KeyRange kr(pos, p.window, p.keep_first, p.chunk);
   const float slope = p.slopes ? p.slopes[h] : 0.f, bias = p.head_bias ? p.head_bias[h] : 0.f;
   float m = p.sigmoid_weights ? 0.f : -INFINITY, l = 0.f, acc[DPL];
 #pragma unroll
@@ -258,7 +298,7 @@ __global__ void __launch_bounds__(128) attention_ragged_split_kernel(RagAttnPara
   __syncthreads();
   const int pos = p.tok_pos[t];
   const int32_t* pt_row = p.page_table + (size_t)p.tok_slot[t] * p.pt_stride;
-  const KeyRange kr(pos, p.window, p.keep_first);
+  const KeyRange kr(pos, p.window, p.keep_first, p.chunk);
   float slope[R], bias[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -408,7 +448,8 @@ static int launch_ragged(const RagAttnParams& p, float* ws, long long ws_floats,
   if (items <= split_max && (p.window <= 0 || p.window > 64)) {
     // key slices until about two CTAs per SM are busy; a slice holds at least 128 keys (one block per warp)
     const long long ctas = (long long)p.n_tokens * (p.H / R);
-    const int span = p.window > 0 ? p.window : 1 << 20;
+    int span = p.window > 0 ? p.window : 1 << 20;
+    if (p.chunk > 0) span = min(span, p.chunk);
     int slices = 1;
     while (slices < 32 && ctas * slices * 2 <= 296 && span / (slices * 2) >= 128 &&
            items * slices * 2 * (2 + 32 * DPL) <= ws_floats) slices *= 2;
@@ -438,7 +479,23 @@ extern "C" int pg_attention_ragged_sink(void* out, int ld_out, const void* q, in
                                         const float* slopes, int sigmoid_weights, const float* head_bias,
                                         const float* sink, float out_scale, float* ws, long long ws_floats, int dtype,
                                         void* stream) {
+  return pg_attention_ragged_masked(out, ld_out, q, ld_q, gate, ld_gate, gate_per_head, k_pool, ld_k, v_pool, ld_v, page_table,
+                                    pt_stride, page_size, tok_slot, tok_pos, n_tokens, n_heads, n_kv_heads, dim, vdim, scale,
+                                    window, keep_first, 0, slopes, sigmoid_weights, head_bias, sink, nullptr, 0, out_scale, ws,
+                                    ws_floats, dtype, stream);
+}
+
+extern "C" int pg_attention_ragged_masked(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                          int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
+                                          const int32_t* page_table, int pt_stride, int page_size,
+                                          const int32_t* tok_slot, const int32_t* tok_pos, int n_tokens, int n_heads,
+                                          int n_kv_heads, int dim, int vdim, float scale, int window, int keep_first,
+                                          int chunk, const float* slopes, int sigmoid_weights, const float* head_bias,
+                                          const float* sink, const float* out_rot, int out_rot_interleaved,
+                                          float out_scale, float* ws, long long ws_floats, int dtype, void* stream) {
   if (n_tokens <= 0) return PG_OK;
+  PG_REQUIRE(chunk >= 0 && (chunk == 0 || keep_first == 0), "attention_ragged: blocks of %d positions with %d kept first ones",
+             chunk, keep_first);
   if (ld_k <= 0) ld_k = n_kv_heads * dim;
   if (ld_v <= 0) ld_v = n_kv_heads * vdim;
   PG_REQUIRE(ld_k >= n_kv_heads * dim && ld_v >= n_kv_heads * vdim, "attention_ragged: pool rows of %d / %d elements", ld_k, ld_v);
@@ -447,7 +504,8 @@ extern "C" int pg_attention_ragged_sink(void* out, int ld_out, const void* q, in
   PG_REQUIRE(dim > 0 && dim <= 1024 && vdim > 0 && vdim <= 512, "attention_ragged: dim %d (<= 1024), vdim %d (<= 512)", dim, vdim);
   RagAttnParams p = {out, ld_out, q, ld_q, gate, ld_gate, k_pool, v_pool, page_table, pt_stride, page_size, tok_slot,
                      tok_pos, n_tokens, n_heads, n_kv_heads, dim, vdim, scale, window, slopes, keep_first,
-                     sigmoid_weights ? 1 : 0, head_bias, gate_per_head ? 1 : 0, out_scale, ld_k, ld_v, sink};
+                     sigmoid_weights ? 1 : 0, head_bias, gate_per_head ? 1 : 0, out_scale, ld_k, ld_v, sink, chunk, out_rot,
+                     out_rot_interleaved ? 1 : 0};
   cudaStream_t st = (cudaStream_t)stream;
   const int dpl = (vdim + 31) / 32;
   PG_DISPATCH_DTYPE(dtype, T, {

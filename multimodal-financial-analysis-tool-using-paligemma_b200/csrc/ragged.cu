@@ -33,11 +33,13 @@ __global__ void embed_pos_kernel(float* __restrict__ x, const int64_t* __restric
 // ------------------------------------------------------------------ residual sum + RMS norm in groups
 // One warp per (row, group).  x[row] += a[row] + b[row] first (either may be absent; the sum is written back), then
 // each of the `groups` equal consecutive parts of the row is divided by its own sqrt(mean(part^2) + eps) and the
-// whole is multiplied by w.  rows_idx (optional) picks the input rows; output rows are packed.
-template <typename T>
-__global__ void group_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ x, const T* __restrict__ a, int lda,
+// whole is multiplied by w (by 1 + w when the weight is stored around zero: one_plus).  rows_idx (optional) picks the
+// input rows; output rows are packed, in the model dtype or (TO = float) unrounded for a consumer that goes on in fp32.
+template <typename T, typename TO>
+__global__ void group_rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, const T* __restrict__ a, int lda,
                                      const T* __restrict__ b, int ldb, const T* __restrict__ w,
-                                     const int32_t* __restrict__ rows_idx, int rows, int D, int groups, float eps) {
+                                     const int32_t* __restrict__ rows_idx, int rows, int D, int groups, float eps,
+                                     int one_plus) {
   pdl_launch_dependents();
   pdl_wait();
   const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -62,8 +64,9 @@ __global__ void group_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ x,
   if (!out) return;
   ss = warp_sum(ss);
   const float inv = 1.f / sqrtf(ss / (float)gs + eps);
-  T* o = out + (size_t)r * D + g * gs;
-  for (int c = lane; c < gs; c += 32) o[c] = from_f<T>(xr[c] * inv * to_f<T>(w[g * gs + c]));
+  TO* o = out + (size_t)r * D + g * gs;
+  const float w0 = one_plus ? 1.f : 0.f;
+  for (int c = lane; c < gs; c += 32) o[c] = from_f<TO>(xr[c] * inv * (w0 + to_f<T>(w[g * gs + c])));
 }
 
 // ------------------------------------------------------------------ query / key norm over the whole projection + cache append
@@ -298,6 +301,80 @@ postnorm_residual_row_kernel(T* __restrict__ out, float* __restrict__ x, const T
   }
 }
 
+// ------------------------------------------------------------------ per-head norms + rotary positions (keys, queries AND values) + cache append
+// One CTA per token, one warp per head (query heads, then key heads, then value heads).  Every query / key head is
+// divided by its own root mean square over `dim` and multiplied by a weight of `dim` entries shared by the heads
+// (q_w / k_w NULL: no norm), then its first rot_dims columns are rotated by position * freq[i] (pairs (2i, 2i+1) when
+// interleaved, else (i, i + rot_dims / 2)).  Every value head is divided by its root mean square over vdim when v_norm
+// is set (no weight) and, with v_freq, rotated over ALL its columns by position * v_freq[m] in the layout v_interleaved
+// names; the attention that reads such values turns its result back by the query's position.  Norm statistics, angles
+// and the rotation are fp32; one rounding when the row is stored.
+template <typename T>
+__global__ void headnorm_rotary_append_kernel(T* __restrict__ q_out, const T* __restrict__ proj, int ld, int q_col0, int H,
+                                              int k_col0, int G, int dim, int v_col0, int vdim, const T* __restrict__ q_w,
+                                              const T* __restrict__ k_w, float eps, const float* __restrict__ freq,
+                                              int rot_dims, int interleaved, int v_norm, const float* __restrict__ v_freq,
+                                              int v_interleaved, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                              const int32_t* __restrict__ page_table, int pt_stride, int page_size,
+                                              const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const T* row = proj + (size_t)t * ld;
+  const int p = tok_pos[t];
+  const float fp = (float)p;
+  const size_t slot_row = (size_t)page_table[(size_t)tok_slot[t] * pt_stride + p / page_size] * page_size + p % page_size;
+  for (int item = warp; item < H + 2 * G; item += warps) {
+    const int kind = item < H ? 0 : (item < H + G ? 1 : 2);
+    const int head = kind == 0 ? item : (kind == 1 ? item - H : item - H - G);
+    const int n = kind == 2 ? vdim : dim;
+    const T* src = row + (kind == 0 ? q_col0 : (kind == 1 ? k_col0 : v_col0)) + head * n;
+    T* dst = kind == 0 ? q_out + (size_t)t * H * dim + head * dim
+                       : (kind == 1 ? k_pool + slot_row * ((size_t)G * dim) + head * dim
+                                    : v_pool + slot_row * ((size_t)G * vdim) + head * vdim);
+    const T* w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
+    const bool normed = kind == 2 ? v_norm != 0 : w != nullptr;
+    const float* f = kind == 2 ? v_freq : freq;
+    const int rd = kind == 2 ? (v_freq ? vdim & ~1 : 0) : rot_dims, il = kind == 2 ? v_interleaved : interleaved;
+    float inv = 1.f;
+    if (normed) {
+      float ss = 0.f;
+      for (int c = lane; c < n; c += 32) { const float v = to_f<T>(src[c]); ss += v * v; }
+      inv = 1.f / sqrtf(warp_sum(ss) / (float)n + eps);
+    }
+    const int half = rd >> 1;
+    for (int i = lane; i < half; i += 32) {
+      const int c0 = il ? 2 * i : i, c1 = il ? 2 * i + 1 : i + half;
+      const float a = to_f<T>(src[c0]) * inv * (w ? to_f<T>(w[c0]) : 1.f), b = to_f<T>(src[c1]) * inv * (w ? to_f<T>(w[c1]) : 1.f);
+      float sn, cs;
+      sincosf(fp * f[i], &sn, &cs);
+      dst[c0] = from_f<T>(a * cs - b * sn);
+      dst[c1] = from_f<T>(b * cs + a * sn);
+    }
+    for (int c = rd + lane; c < n; c += 32) dst[c] = from_f<T>(to_f<T>(src[c]) * inv * (w ? to_f<T>(w[c]) : 1.f));
+  }
+}
+
+// ------------------------------------------------------------------ squared ReLU
+template <typename T>
+__global__ void relu2_kernel(T* __restrict__ out, const T* __restrict__ z, long long n, int vec) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int V = Vec<T>::N;
+  const long long stride = (long long)gridDim.x * blockDim.x, first = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (vec) {
+    for (long long i = first; i < n / V; i += stride) {
+      float f[V];
+      unpack<T>(*reinterpret_cast<const uint4*>(z + i * V), f);
+#pragma unroll
+      for (int k = 0; k < V; ++k) { const float r = fmaxf(f[k], 0.f); f[k] = r * r; }
+      *reinterpret_cast<uint4*>(out + i * V) = pack<T>(f);
+    }
+    return;
+  }
+  for (long long i = first; i < n; i += stride) { const float r = fmaxf(to_f<T>(z[i]), 0.f); out[i] = from_f<T>(r * r); }
+}
+
 }  // namespace pg
 
 using namespace pg;
@@ -316,15 +393,25 @@ extern "C" int pg_embed_pos(float* x, const int64_t* ids, const int32_t* positio
 extern "C" int pg_group_rmsnorm(void* out, float* x, const void* add_a, int lda, const void* add_b, int ldb,
                                 const void* w, const int32_t* rows_idx, int rows, int D, int groups, float eps,
                                 int dtype, void* stream) {
+  return pg_group_rmsnorm_ex(out, x, add_a, lda, add_b, ldb, w, rows_idx, rows, D, groups, eps, 0, 0, dtype, stream);
+}
+
+extern "C" int pg_group_rmsnorm_ex(void* out, float* x, const void* add_a, int lda, const void* add_b, int ldb,
+                                   const void* w, const int32_t* rows_idx, int rows, int D, int groups, float eps,
+                                   int one_plus, int out_f32, int dtype, void* stream) {
   if (rows <= 0) return PG_OK;
   PG_REQUIRE(groups >= 1 && D % groups == 0, "group_rmsnorm: D=%d is not a multiple of groups=%d", D, groups);
   PG_REQUIRE(!out || w, "group_rmsnorm: a normalised output needs a weight");
   PG_REQUIRE(!rows_idx || (!add_a && !add_b), "group_rmsnorm: the residual sum takes all rows (no row index)");
   const int warps = 8;
   PG_DISPATCH_DTYPE(dtype, T, {
-    return launch_pdl("group_rmsnorm", group_rmsnorm_kernel<T>, dim3(cdiv((long long)rows * groups, warps)), dim3(warps * 32),
+    if (out_f32)
+      return launch_pdl("group_rmsnorm", group_rmsnorm_kernel<T, float>, dim3(cdiv((long long)rows * groups, warps)),
+                        dim3(warps * 32), 0, (cudaStream_t)stream, (float*)out, x, (const T*)add_a, lda, (const T*)add_b, ldb,
+                        (const T*)w, rows_idx, rows, D, groups, eps, one_plus);
+    return launch_pdl("group_rmsnorm", group_rmsnorm_kernel<T, T>, dim3(cdiv((long long)rows * groups, warps)), dim3(warps * 32),
                       0, (cudaStream_t)stream, (T*)out, x, (const T*)add_a, lda, (const T*)add_b, ldb, (const T*)w, rows_idx,
-                      rows, D, groups, eps);
+                      rows, D, groups, eps, one_plus);
   });
   return PG_OK;
 }
@@ -434,6 +521,41 @@ extern "C" int pg_postnorm_residual(void* out, float* x, const void* y, int ldy,
     return launch_pdl("postnorm_residual", postnorm_residual_kernel<T>, dim3(cdiv(rows, warps)), dim3(warps * 32), 0,
                       (cudaStream_t)stream, (T*)out, x, (const T*)y, ldy, (const T*)w_post, (const T*)scale,
                       (const T*)w_next, rows, D, eps);
+  });
+  return PG_OK;
+}
+
+extern "C" int pg_headnorm_rotary_append(void* q_out, const void* proj, int ld, int q_col0, int n_heads, int k_col0,
+                                         int n_kv_heads, int dim, int v_col0, int vdim, const void* q_w, const void* k_w,
+                                         float eps, const float* freq, int rot_dims, int interleaved, int v_norm,
+                                         const float* v_freq, int v_interleaved, void* k_pool, void* v_pool,
+                                         const int32_t* page_table, int pt_stride, int page_size, const int32_t* tok_slot,
+                                         const int32_t* tok_pos, int n_tokens, int dtype, void* stream) {
+  if (n_tokens <= 0) return PG_OK;
+  PG_REQUIRE(q_out && proj && k_pool && v_pool && page_table && tok_slot && tok_pos && page_size > 0,
+             "headnorm_rotary_append: pools and token map");
+  PG_REQUIRE(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || freq),
+             "headnorm_rotary_append: %d rotated columns of %d (even, with a frequency table)", rot_dims, dim);
+  PG_REQUIRE(!v_freq || vdim % 2 == 0, "headnorm_rotary_append: rotated values need an even width, not %d", vdim);
+  const int heads = n_heads + 2 * n_kv_heads;
+  const int threads = heads >= 16 ? 512 : (heads >= 8 ? 256 : 128);
+  PG_DISPATCH_DTYPE(dtype, T, {
+    return launch_pdl("headnorm_rotary_append", headnorm_rotary_append_kernel<T>, dim3(n_tokens), dim3(threads), 0,
+                      (cudaStream_t)stream, (T*)q_out, (const T*)proj, ld, q_col0, n_heads, k_col0, n_kv_heads, dim, v_col0,
+                      vdim, (const T*)q_w, (const T*)k_w, eps, freq, rot_dims, interleaved, v_norm, v_freq, v_interleaved,
+                      (T*)k_pool, (T*)v_pool, page_table, pt_stride, page_size, tok_slot, tok_pos);
+  });
+  return PG_OK;
+}
+
+extern "C" int pg_relu2(void* out, const void* z, long long n, int dtype, void* stream) {
+  if (n <= 0) return PG_OK;
+  PG_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = Vec<T>::N;
+    const int vec = (n % V == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)z % 16) == 0) ? 1 : 0;
+    const long long work = vec ? n / V : n;
+    const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
+    return launch_pdl("relu2", relu2_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out, (const T*)z, n, vec);
   });
   return PG_OK;
 }

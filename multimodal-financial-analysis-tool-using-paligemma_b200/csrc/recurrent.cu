@@ -300,11 +300,15 @@ __global__ void lightning_prep_kernel(float* __restrict__ rec, const T* __restri
   }
 }
 
-template <int DMAX, int RG, int CH>
+//                                       TD (decay per token): the record carries four more floats [decay, 0, 0, 0] after
+//                                       the values and the decay of a token comes from there instead of decay[h];
+//                                       skip (may be NULL): skip[h] * v is added to the output (the state-space
+//                                       mixer's direct term, with v its unscaled input).
+template <int DMAX, int RG, int CH, bool TD>
 __global__ void __launch_bounds__(256)
 lightning_kernel(float* __restrict__ out, float* __restrict__ state, const float* __restrict__ rec,
-                 const float* __restrict__ decay, const int32_t* __restrict__ segs, int heads, int dim, int vdim, int dp,
-                 int vp) {
+                 const float* __restrict__ decay, const float* __restrict__ skip, const int32_t* __restrict__ segs,
+                 int heads, int dim, int vdim, int dp, int vp) {
   constexpr int NG = DMAX / (4 * RG);               // groups of four rows per thread (RG lanes share a value column)
   extern __shared__ __align__(16) float sh[];       // [2][CH][q DMAX | k DMAX | v VT]
   pdl_launch_dependents();
@@ -312,10 +316,11 @@ lightning_kernel(float* __restrict__ out, float* __restrict__ state, const float
   const int32_t* sg = segs + 3 * (size_t)blockIdx.x;
   const int slot = sg[0], row0 = sg[1], n = sg[2];
   if (n <= 0) return;
-  const int VT = blockDim.x / RG, RSZ = 2 * DMAX + VT, rs = 2 * dp + vp;
+  constexpr int XP = TD ? 4 : 0;
+  const int VT = blockDim.x / RG, RSZ = 2 * DMAX + VT + XP, rs = 2 * dp + vp + XP;
   const int h = blockIdx.y, j0 = blockIdx.z * VT, jl = threadIdx.x / RG, j = j0 + jl, rg = threadIdx.x % RG;
   const bool live = j < vdim;
-  const float lam = decay[h];
+  const float lam_h = TD ? 0.f : decay[h], skip_h = skip ? skip[h] : 0.f;
   for (int idx = threadIdx.x; idx < 2 * CH * RSZ; idx += blockDim.x) sh[idx] = 0.f;   // padding the copies never write
   float S[NG * 4];
   float* st = state + ((size_t)slot * heads + h) * dim * vdim;
@@ -327,7 +332,7 @@ lightning_kernel(float* __restrict__ out, float* __restrict__ state, const float
       S[m * 4 + e] = (live && i < dim) ? st[(size_t)i * vdim + j] : 0.f;
     }
   __syncthreads();
-  const int qk_pieces = dp / 4, v_pieces = min(VT, vp - j0) / 4, pieces = 2 * qk_pieces + v_pieces;
+  const int qk_pieces = dp / 4, v_pieces = min(VT, vp - j0) / 4, pieces = 2 * qk_pieces + v_pieces + (TD ? 1 : 0);
   auto fetch = [&](int t0, int buf) {               // records of tokens [t0, t0 + CH) of this head -> buffer buf
     const int nt = min(CH, n - t0);
     for (int idx = threadIdx.x; idx < nt * pieces; idx += blockDim.x) {
@@ -336,7 +341,8 @@ lightning_kernel(float* __restrict__ out, float* __restrict__ state, const float
       float* dst = sh + ((size_t)buf * CH + tt) * RSZ;
       if (pc < qk_pieces) cp_async16(dst + pc * 4, src + pc * 4);
       else if (pc < 2 * qk_pieces) cp_async16(dst + DMAX + (pc - qk_pieces) * 4, src + dp + (pc - qk_pieces) * 4);
-      else cp_async16(dst + 2 * DMAX + (pc - 2 * qk_pieces) * 4, src + 2 * dp + j0 + (pc - 2 * qk_pieces) * 4);
+      else if (pc < 2 * qk_pieces + v_pieces) cp_async16(dst + 2 * DMAX + (pc - 2 * qk_pieces) * 4, src + 2 * dp + j0 + (pc - 2 * qk_pieces) * 4);
+      else cp_async16(dst + 2 * DMAX + VT, src + 2 * dp + vp);
     }
     cp_async_commit();
   };
@@ -350,6 +356,7 @@ lightning_kernel(float* __restrict__ out, float* __restrict__ state, const float
     for (int tt = 0; tt < nt; ++tt) {
       const float* r = sh + ((size_t)buf * CH + tt) * RSZ;
       const float vj = r[2 * DMAX + jl];
+      const float lam = TD ? r[2 * DMAX + VT] : lam_h;
       const float* qr = r + 4 * rg;
       const float* kr = r + DMAX + 4 * rg;
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
@@ -367,7 +374,7 @@ lightning_kernel(float* __restrict__ out, float* __restrict__ state, const float
       float o = (o0 + o1) + (o2 + o3);
 #pragma unroll
       for (int sh_ = 1; sh_ < RG; sh_ <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh_);
-      if (live && rg == 0) out[((size_t)row0 + t0 + tt) * heads * vdim + h * vdim + j] = o;
+      if (live && rg == 0) out[((size_t)row0 + t0 + tt) * heads * vdim + h * vdim + j] = fmaf(skip_h, vj, o);
     }
     __syncthreads();                                // every thread is done with this buffer before it is refilled
   }
@@ -383,8 +390,8 @@ lightning_kernel(float* __restrict__ out, float* __restrict__ state, const float
 }
 
 template <int DMAX, int RG, int CH>
-static int launch_lightning(float* out, float* state, const float* rec, const float* decay, const int32_t* segs, int n_segs,
-                            int heads, int dim, int vdim, cudaStream_t st) {
+static int launch_lightning(float* out, float* state, const float* rec, const float* decay, const float* skip, bool td,
+                            const int32_t* segs, int n_segs, int heads, int dim, int vdim, cudaStream_t st) {
   const int dp = (dim + 3) / 4 * 4, vp = (vdim + 3) / 4 * 4;
   // value columns per CTA: as many as 256 threads hold for prompt-sized work (few fat CTAs, about one per SM, beat
   // many thin ones: 0.75 against 0.87 ms at 4 x 2048 tokens, 8 heads of 128), fewer while the CTAs do not fill the SMs
@@ -392,12 +399,16 @@ static int launch_lightning(float* out, float* state, const float* rec, const fl
   while (vt > 8 && (vt / 2 >= vdim || (long long)n_segs * heads * cdiv(vdim, vt) < 100)) vt /= 2;
   static const int vt_env = env_int("PG_LIGHTNING_VT", 0);
   if (vt_env >= 8 && vt_env <= 256 / RG && (vt_env & (vt_env - 1)) == 0) vt = vt_env;
-  const size_t smem = sizeof(float) * 2 * CH * (2 * DMAX + vt);
+  const size_t smem = sizeof(float) * 2 * CH * (2 * DMAX + vt + (td ? 4 : 0));
   // An ordinary launch, not a programmatic dependent one: CTAs that become resident while the preceding kernel still
   // fills the machine are placed on the few SMs with room, and a recurrence of a few hundred long-lived CTAs then runs
   // on a fraction of the GPU (measured at 4 x 2048 tokens, 8 heads of 128: 2.06 ms against 0.88 ms).
-  lightning_kernel<DMAX, RG, CH><<<dim3(n_segs, heads, cdiv(vdim, vt)), dim3(vt * RG), smem, st>>>(
-      out, state, rec, decay, segs, heads, dim, vdim, dp, vp);
+  if (td)
+    lightning_kernel<DMAX, RG, CH, true><<<dim3(n_segs, heads, cdiv(vdim, vt)), dim3(vt * RG), smem, st>>>(
+        out, state, rec, decay, skip, segs, heads, dim, vdim, dp, vp);
+  else
+    lightning_kernel<DMAX, RG, CH, false><<<dim3(n_segs, heads, cdiv(vdim, vt)), dim3(vt * RG), smem, st>>>(
+        out, state, rec, decay, skip, segs, heads, dim, vdim, dp, vp);
   return check_launch("lightning");
 }
 
@@ -485,14 +496,20 @@ extern "C" int pg_lightning_prep(float* rec, const void* proj, int ld, int q_col
 
 extern "C" int pg_lightning_attention(float* out, float* state, const float* rec, const float* decay, const int32_t* segs,
                                       int n_segs, int heads, int dim, int vdim, void* stream) {
+  return pg_lightning_attention_ex(out, state, rec, decay, nullptr, segs, n_segs, heads, dim, vdim, stream);
+}
+
+extern "C" int pg_lightning_attention_ex(float* out, float* state, const float* rec, const float* decay, const float* skip,
+                                         const int32_t* segs, int n_segs, int heads, int dim, int vdim, void* stream) {
   if (n_segs <= 0) return PG_OK;
-  PG_REQUIRE(out && state && rec && decay && segs, "lightning_attention: bad arguments");
+  const bool td = decay == nullptr;                 // no constant decay: the records carry one per token
+  PG_REQUIRE(out && state && rec && segs, "lightning_attention: bad arguments");
   PG_REQUIRE(dim > 0 && dim <= 256 && vdim > 0, "lightning_attention: key size %d (1..256), value size %d", dim, vdim);
   cudaStream_t st = (cudaStream_t)stream;
   // lanes per value column: a thread keeps DMAX / RG state elements, and a token is that many fused multiply-adds
   // twice plus log2(RG) shuffle steps on the critical path of the recurrence
-  if (dim <= 32) return launch_lightning<32, 4, 16>(out, state, rec, decay, segs, n_segs, heads, dim, vdim, st);
-  if (dim <= 64) return launch_lightning<64, 8, 8>(out, state, rec, decay, segs, n_segs, heads, dim, vdim, st);
-  if (dim <= 128) return launch_lightning<128, 8, 8>(out, state, rec, decay, segs, n_segs, heads, dim, vdim, st);
-  return launch_lightning<256, 16, 4>(out, state, rec, decay, segs, n_segs, heads, dim, vdim, st);
+  if (dim <= 32) return launch_lightning<32, 4, 16>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
+  if (dim <= 64) return launch_lightning<64, 8, 8>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
+  if (dim <= 128) return launch_lightning<128, 8, 8>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
+  return launch_lightning<256, 16, 4>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
 }

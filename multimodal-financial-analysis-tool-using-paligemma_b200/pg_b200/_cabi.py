@@ -108,9 +108,22 @@ SIGNATURES = {
     "pg_concat_cast": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "pg_attention_ragged_tc_sink": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i,
                                     _i, _i, _f, _i, _i, _vp, _i, _vp, _vp, _f, _vp, _i, _vp],
+    # norms stored around zero, convolutions over time, per-head norms + rotated values, blocked masks, state-space mixer
+    "pg_group_rmsnorm_ex": [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _vp],
+    "pg_time_conv_residual": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pg_time_conv_state": [_vp, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _vp],
+    "pg_headnorm_rotary_append": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _i, _i, _vp, _i, _vp, _vp,
+                                  _vp, _i, _i, _vp, _vp, _i, _i, _vp],
+    "pg_attention_ragged_masked": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i,
+                                   _i, _f, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _ll, _i, _vp],
+    "pg_relu2": [_vp, _vp, _ll, _i, _vp],
+    "pg_ssm_record_floats": [_i, _i, _i, _i],
+    "pg_ssm_prep": [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "pg_gate_groupnorm": [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _f, _i, _vp],
+    "pg_lightning_attention_ex": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
 }
 _RESTYPE = {"pg_last_error": C.c_char_p, "pg_launch_count": _ull, "pg_decode_attention_ws_floats": _ll,
-            "pg_delta_record_floats": _ll, "pg_lightning_record_floats": _ll}
+            "pg_delta_record_floats": _ll, "pg_lightning_record_floats": _ll, "pg_ssm_record_floats": _ll}
 
 _lib = None
 

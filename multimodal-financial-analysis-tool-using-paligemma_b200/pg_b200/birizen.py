@@ -46,7 +46,8 @@ import torch
 
 from . import _cabi as cabi
 from ._cabi import ptr
-from .ragged_engine import RaggedEngine, RotaryCfg, StepInputs, _stack_rows
+from .latent import LatentAttentionMixin, LatentCfg, latent_cfg, pack_latent
+from .ragged_engine import RaggedEngine, StepInputs, _stack_rows
 from .registry import register
 
 GLU_ALPHA = 1.702                 # the sigmoid's slope in the experts' activation: fixed by the design
@@ -58,18 +59,6 @@ class LightningCfg:
     dim: int
     vdim: int
     decay: List[float]
-
-
-@dataclass
-class LatentCfg:
-    heads: int
-    dim: int                      # plain (unrotated) query / key columns per head
-    rot_dim: int                  # rotated columns per head (one key part shared by the heads)
-    vdim: int
-    q_rank: int
-    kv_rank: int
-    scale: float
-    rot: RotaryCfg
 
 
 @dataclass
@@ -135,13 +124,7 @@ class BirizenConfig:
                     raise ValueError(f"layer {i}: {len(decay)} decays for {heads} heads")
                 mixer = LightningCfg(heads, int(m["dim"]), int(m.get("vdim", m["dim"])), decay)
             elif kind == "latent_attention":
-                rot_dim = int(m["rot_dim"])
-                rot = m.get("rot") or {}
-                rc = RotaryCfg(int(rot.get("dims", rot_dim)), float(rot["base"]), rot.get("scaling")) if rot_dim else None
-                if rc is not None and (rc.dims != rot_dim or rot_dim % 2):
-                    raise ValueError(f"layer {i}: {rc.dims} rotary columns for a rotated part of {rot_dim}")
-                mixer = LatentCfg(int(m["heads"]), int(m["dim"]), rot_dim, int(m["vdim"]), int(m["q_rank"]),
-                                  int(m["kv_rank"]), float(m["scale"]), rc)
+                mixer = latent_cfg(i, m)
             else:
                 raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
             ml = L.get("mlp")
@@ -170,7 +153,7 @@ class BirizenConfig:
 
 
 @register("Birizen")
-class BirizenEngine(RaggedEngine):
+class BirizenEngine(LatentAttentionMixin, RaggedEngine):
     """Weights + paged latent pools + recurrent state shapes + the launch sequence of one step over a ragged batch."""
 
     def __init__(self, config, weights: Mapping[str, torch.Tensor], *, device="cuda", dtype=torch.bfloat16,
@@ -179,14 +162,10 @@ class BirizenEngine(RaggedEngine):
         self.strict = bool(strict)      # True: tensors the config does not call for raise instead of being reported
         self._init_common(device=device, dtype=dtype, page_size=page_size, gemm_impl=gemm_impl)
         self.runs = self.cfg.runs()
-        self.head_impl = 0              # per-head products of latent attention: 0 = tensor cores where they fit, 1 = fp32 FMA
         self.needs_segments = any(self.cfg.layers[r.layer].kind == "lightning" for r in self.runs)
         self._repack(weights)
         for w, lc in zip(self.layers, self.cfg.layers):     # prompt portions of latent layers whose sizes the tensor-core kernel takes
-            a = lc.mixer
-            w["attn_tc"] = lc.kind == "latent_attention" and bool(cabi.lib().pg_attention_ragged_tc_ok(
-                a.kv_rank + a.rot_dim, a.kv_rank, self.page_size, a.heads * (a.kv_rank + a.rot_dim), a.heads * a.kv_rank, 8,
-                self.dt))
+            w["attn_tc"] = lc.kind == "latent_attention" and self._latent_tc_ok(lc.mixer)
         self._attn_tc_any = any(w["attn_tc"] for w in self.layers)
         self._init_runtime(kv_pool_tokens)
         # one latent pool per RUN of a latent layer: a layer that runs twice keeps two caches
@@ -227,22 +206,7 @@ class BirizenEngine(RaggedEngine):
                 w.update(onorm=W(m + "norm", (nv,)), o=W(m + "o", (D, nv)),
                          decay=torch.tensor(a.decay, dtype=torch.float32, device=self.device))
             else:
-                a = L.mixer
-                hq, hv = a.heads * (a.dim + a.rot_dim), a.heads * a.vdim
-                w["proj"], w["at"] = _stack_rows([("dq", W(m + "dq", (a.q_rank, D))),
-                                                  ("dkv", W(m + "dkv", (a.kv_rank + a.rot_dim, D))),
-                                                  ("g", W(m + "g", (hv, D)))], self.device, self.dtype)
-                # Wuk per head, transposed: the query of a head is taken into the latent space by [kv_rank, dim]
-                uk_t = W(m + "uk", (a.heads * a.dim, a.kv_rank)).view(a.heads, a.dim, a.kv_rank).transpose(1, 2).contiguous()
-                w.update(dq_norm=W(m + "dq.norm", (a.q_rank,)), dkv_norm=W(m + "dkv.norm", (a.kv_rank,)),
-                         uq=W(m + "uq", (hq, a.q_rank)), uk_t=uk_t, uv=W(m + "uv", (hv, a.kv_rank)),
-                         sink=W(m + "sink", (a.heads,), torch.float32), o=W(m + "o", (D, hv)),
-                         ld_pool=(a.kv_rank + a.rot_dim + 7) // 8 * 8)
-                if a.rot is not None:
-                    f, mag = a.rot.table()
-                    w["freq"], w["mag"] = f.to(torch.float32).to(self.device), float(mag)
-                else:
-                    w["freq"], w["mag"] = None, 1.0
+                w.update(pack_latent(W, m, L.mixer, D, self.device, self.dtype, gated=True))
             ml = L.mlp
             if ml is not None:
                 f = p + "mlp."
@@ -308,53 +272,6 @@ class BirizenEngine(RaggedEngine):
         with tm("o"):
             return self._linear(att, w["o"])
 
-    def _per_head(self, out, o_hs: int, a, a_hs: int, w, gate, heads: int, N: int, K: int) -> None:
-        """out[t, h * o_hs + n] = sum_k a[t, h * a_hs + k] w[h, n, k] (* sigmoid(gate[t, h * N + n])) for every head:
-        prompt-sized 16-bit steps as ONE launch of the experts' grouped tensor-core GEMM with the heads as its groups,
-        a handful of rows, fp32 and sizes that kernel does not take on the per-head kernels of the latent-attention file."""
-        cabi.check(cabi.lib().pg_head_gemm_ex(ptr(out), out.stride(0), o_hs, ptr(a), a.stride(0), a_hs, ptr(w), ptr(gate),
-                                              0 if gate is None else gate.stride(0), a.shape[0], heads, N, K, self.head_impl,
-                                              ptr(self.err_flag), self.dt, cabi.stream()), "head_gemm")
-
-    def _latent(self, kv, inp: StepInputs, ri: int, a: LatentCfg, w: dict, h) -> torch.Tensor:
-        L, st, tm, T, at = cabi.lib(), cabi.stream(), self._tm, inp.T, w["at"]
-        pool, ldp = self.c_pools[ri], w["ld_pool"]
-        with tm("proj"):
-            proj = self._linear(h, w["proj"])
-        cq = self._new(T, a.q_rank)
-        with tm("latent_prep"):
-            cabi.check(L.pg_latent_prep(ptr(cq), ptr(proj), proj.stride(0), at["dq"], a.q_rank, ptr(w["dq_norm"]), at["dkv"],
-                                        a.kv_rank, ptr(w["dkv_norm"]), a.rot_dim, ptr(w["freq"]), w["mag"], self.cfg.eps,
-                                        ptr(pool), ldp, ptr(kv.page_table), kv.max_pages, self.page_size, ptr(inp.slot),
-                                        ptr(inp.pos), T, self.dt, st), "latent_prep")
-        with tm("q_up"):
-            q = self._linear(cq, w["uq"])
-        hd, ld_q = a.dim + a.rot_dim, a.kv_rank + a.rot_dim
-        qa = self._new(T, a.heads * ld_q)
-        with tm("q_absorb"):
-            self._per_head(qa, ld_q, q, hd, w["uk_t"], None, a.heads, a.kv_rank, a.dim)
-            cabi.check(L.pg_rotary_cols(ptr(qa), qa.stride(0), a.kv_rank, ld_q, ptr(q), q.stride(0), a.dim, hd, a.heads,
-                                        a.rot_dim, ptr(w["freq"]), w["mag"], ptr(inp.pos), T, self.dt, st), "rotary_cols")
-        ol = self._new(T, a.heads * a.kv_rank)
-        with tm("latent_attention"):
-            if inp.n_tiles and w["attn_tc"]:
-                cabi.check(L.pg_attention_ragged_tc_sink(
-                    ptr(ol), ol.stride(0), ptr(qa), qa.stride(0), None, 0, 0, ptr(pool), ldp, ptr(pool), ldp,
-                    self.num_pages * self.page_size, ptr(kv.page_table), kv.max_pages, self.page_size, ptr(inp.tiles),
-                    inp.n_tiles, T, a.heads, 1, ld_q, a.kv_rank, a.scale, 0, 0, None, 0, None, ptr(w["sink"]), 1.0,
-                    ptr(self.err_flag), self.dt, st), "attention_ragged_tc_sink")
-            else:
-                cabi.check(L.pg_attention_ragged_sink(
-                    ptr(ol), ol.stride(0), ptr(qa), qa.stride(0), None, 0, 0, ptr(pool), ldp, ptr(pool), ldp,
-                    ptr(kv.page_table), kv.max_pages, self.page_size, ptr(inp.slot), ptr(inp.pos), T, a.heads, 1, ld_q,
-                    a.kv_rank, a.scale, 0, 0, None, 0, None, ptr(w["sink"]), 1.0, ptr(self.attn_ws),
-                    self.attn_ws.numel(), self.dt, st), "attention_ragged_sink")
-        att = self._new(T, a.heads * a.vdim)
-        with tm("v_up_gate"):
-            self._per_head(att, a.vdim, ol, a.kv_rank, w["uv"], proj[:, at["g"]:], a.heads, a.vdim, a.kv_rank)
-        with tm("o"):
-            return self._linear(att, w["o"])
-
     def _moe(self, h, ml: MoeCfg, w: dict) -> torch.Tensor:
         """The feed-forward's output (model dtype): weighted sum of the chosen experts + the shared expert."""
         L, st, tm = cabi.lib(), cabi.stream(), self._tm
@@ -405,7 +322,7 @@ class BirizenEngine(RaggedEngine):
             if lc.kind == "lightning":
                 y = self._lightning(kv, inp, ri, lc.mixer, w, h)
             else:
-                y = self._latent(kv, inp, ri, lc.mixer, w, h)
+                y = self._latent(kv, inp, self.c_pools[ri], lc.mixer, w, h)
             nxt = None                                     # the input norm of the coming run, unless a pass opens there
             if ri + 1 < len(self.runs) and self.runs[ri + 1].loop_pass is None:
                 nxt = self.layers[self.runs[ri + 1].layer]["norm1"]

@@ -49,17 +49,20 @@ class StepInputs:
 class RotaryCfg:
     dims: int
     base: float
-    scaling: Optional[dict] = None       # YaRN: factor, original, fast, slow
+    scaling: Optional[dict] = None       # YaRN: factor, original, fast, slow; linear: factor alone
 
     def table(self):
         """(frequencies float64 [dims / 2], magnitude): angle of pair i at position p = p * f_i; with YaRN scaling the
         slow pairs are interpolated (f / factor), the fast ones kept, a linear ramp in between, and cos / sin are
-        both multiplied by 0.1 ln(factor) + 1."""
+        both multiplied by 0.1 ln(factor) + 1.  A scaling entry that gives a factor alone is linear scaling: every
+        frequency is divided by the factor, the magnitude stays 1."""
         i = torch.arange(self.dims // 2, dtype=torch.float64)
         f = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / self.dims)
         mag = 1.0
         sc = self.scaling
-        if sc:
+        if sc and "original" not in sc:
+            f = f / float(sc["factor"])
+        elif sc:
             factor, orig = float(sc["factor"]), float(sc["original"])
 
             def pair_of(turns: float) -> float:     # the pair index that makes `turns` full turns over `orig` positions

@@ -34,6 +34,7 @@ def architectures() -> List[str]:
 
 def _load_builtin() -> None:
     from . import birizen  # noqa: F401  (registers itself)
+    from . import gogivik  # noqa: F401
     from . import mubasun  # noqa: F401
     from . import ninisun  # noqa: F401
     from . import engine   # noqa: F401
