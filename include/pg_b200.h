@@ -536,6 +536,15 @@ int pg_attention_ragged_masked(void* out, int ld_out, const void* q, int ld_q, c
                                int sigmoid_weights, const float* head_bias, const float* sink, const float* out_rot,
                                int out_rot_interleaved, float out_scale, float* ws, long long ws_floats, int dtype,
                                void* stream);
+/* pg_attention_ragged_tc_sink with the block mask and the turning back of pg_attention_ragged_masked (vdim is a multiple
+ * of 64 here, so both pair layouts fall on whole 32-column loads of the accumulator). */
+int pg_attention_ragged_tc_masked(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                  int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
+                                  long long pool_rows, const int32_t* page_table, int pt_stride, int page_size,
+                                  const int32_t* tiles, int n_tiles, int n_tokens, int n_heads, int n_kv_heads, int dim,
+                                  int vdim, float scale, int window, int keep_first, int chunk, const float* slopes,
+                                  int sigmoid_weights, const float* head_bias, const float* sink, const float* out_rot,
+                                  int out_rot_interleaved, float out_scale, int* err_flag, int dtype, void* stream);
 int pg_relu2(void* out, const void* z, long long n, int dtype, void* stream);
 long long pg_ssm_record_floats(int n_tokens, int heads, int vdim, int state);
 int pg_ssm_prep(float* rec, const void* proj, int ld, int xbc_col0, int dt_col0, const void* conv_w, const void* conv_b,

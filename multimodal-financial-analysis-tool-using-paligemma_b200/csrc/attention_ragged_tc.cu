@@ -57,6 +57,9 @@ struct WinParams {
   int gate_per_head;
   float out_scale;
   const float* sink;             // per query head: exp(sink[h]) joins the softmax denominator (NULL: none)
+  int chunk;                     // > 0: a key is visible only inside the query's block of `chunk` positions
+  const float* out_rot;          // [vdim / 2]: the result is turned back by -position * out_rot[m] (rotated values)
+  int out_rot_interleaved;       // pairs (2m, 2m + 1) instead of (m, m + vdim / 2)
 };
 
 template <typename T>
@@ -107,7 +110,8 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const int32_t* tile = p.tiles + 4 * (size_t)blockIdx.x;
   const int row0 = tile[0], rows = tile[1], slot = tile[2], pos0 = tile[3];
   const int hi = pos0 + rows - 1;                                        // last key position any row can see
-  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;         // first one
+  int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;               // first one
+  if (p.chunk > 0) lo = max(lo, pos0 / p.chunk * p.chunk);               // the block of the tile's first row
   const int t_lo = lo / WK;
   // pages of the kept first positions that lie before the window's first page, then the window's pages
   const int n_keep = (p.keep_first > 0 && p.window > 0) ? min((p.keep_first + WK - 1) / WK, t_lo) : 0;
@@ -170,6 +174,7 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const uint32_t t_row = tmem_base + ((uint32_t)(qw * 32) << 16);
     const int i = pos0 + r;                                        // this row's position
     const float slope = p.slopes ? p.slopes[h] : 0.f, hbias = p.head_bias ? p.head_bias[h] : 0.f;
+    const int blk0 = p.chunk > 0 ? i / p.chunk * p.chunk : 0;      // first position of this row's block
     float m = -INFINITY, l = 0.f;
     int it = 0;
     bool ok = true;
@@ -187,7 +192,7 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
 #pragma unroll
           for (int jj = 0; jj < 32; ++jj) {
             const int j = j0 + c * 32 + jj, back = i - j;
-            const bool vis = back >= 0 && (p.window <= 0 || back < p.window || j < p.keep_first);
+            const bool vis = back >= 0 && j >= blk0 && (p.window <= 0 || back < p.window || j < p.keep_first);
             s[jj] = vis ? s[jj] * p.scale - slope * (float)back + hbias : -INFINITY;
           }
           if (pass == 0) {
@@ -225,24 +230,66 @@ attention_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       const T* grow = (p.gate && !p.gate_per_head) ? reinterpret_cast<const T*>(p.gate) + trow * p.ld_gate + (size_t)h * p.vdim : nullptr;
       if (p.gate && p.gate_per_head && r < rows)
         inv *= 1.f / (1.f + __expf(-to_f<T>(reinterpret_cast<const T*>(p.gate)[trow * p.ld_gate + h])));
-#pragma unroll 1
-      for (int c = 0; c * 32 < p.vdim; ++c) {
-        float o[32];
-        tmem_ld32(t_row + O_COL + c * 32, o);
-        tmem_ld_wait();
-        if (r < rows) {
+      auto store32 = [&](int c, const float* o) {                  // 32 finished columns of this row: gate, round, store
+        if (r >= rows) return;
 #pragma unroll
-          for (int q0 = 0; q0 < 32; q0 += 8) {
-            float w[8], gt[8];
-            if (grow) unpack<T>(*reinterpret_cast<const uint4*>(grow + c * 32 + q0), gt);
+        for (int q0 = 0; q0 < 32; q0 += 8) {
+          float w[8], gt[8];
+          if (grow) unpack<T>(*reinterpret_cast<const uint4*>(grow + c * 32 + q0), gt);
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-              float v = o[q0 + jj] * inv;
-              if (grow) v *= 1.f / (1.f + __expf(-gt[jj]));
-              w[jj] = v;
-            }
-            *reinterpret_cast<uint4*>(orow + c * 32 + q0) = pack<T>(w);
+          for (int jj = 0; jj < 8; ++jj) {
+            float v = o[q0 + jj];
+            if (grow) v *= 1.f / (1.f + __expf(-gt[jj]));
+            w[jj] = v;
           }
+          *reinterpret_cast<uint4*>(orow + c * 32 + q0) = pack<T>(w);
+        }
+      };
+      const float fpos = (float)i;
+      if (!p.out_rot) {
+#pragma unroll 1
+        for (int c = 0; c * 32 < p.vdim; ++c) {
+          float o[32];
+          tmem_ld32(t_row + O_COL + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) o[jj] *= inv;
+          store32(c, o);
+        }
+      } else if (p.out_rot_interleaved) {                          // pairs of neighbours: both halves in one load
+#pragma unroll 1
+        for (int c = 0; c * 32 < p.vdim; ++c) {
+          float o[32];
+          tmem_ld32(t_row + O_COL + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            float sn, cs;
+            sincosf(-fpos * p.out_rot[c * 16 + k], &sn, &cs);
+            const float u = o[2 * k] * inv, v = o[2 * k + 1] * inv;
+            o[2 * k] = u * cs - v * sn;
+            o[2 * k + 1] = v * cs + u * sn;
+          }
+          store32(c, o);
+        }
+      } else {                                                     // column m with m + vdim / 2 (vdim is a multiple of 64)
+        const int hc = p.vdim / 64;
+#pragma unroll 1
+        for (int c = 0; c < hc; ++c) {
+          float a[32], b[32];
+          tmem_ld32(t_row + O_COL + c * 32, a);
+          tmem_ld32(t_row + O_COL + (hc + c) * 32, b);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            float sn, cs;
+            sincosf(-fpos * p.out_rot[c * 32 + jj], &sn, &cs);
+            const float u = a[jj] * inv, v = b[jj] * inv;
+            a[jj] = u * cs - v * sn;
+            b[jj] = v * cs + u * sn;
+          }
+          store32(c, a);
+          store32(hc + c, b);
         }
       }
     }
@@ -279,7 +326,23 @@ extern "C" int pg_attention_ragged_tc_sink(void* out, int ld_out, const void* q,
                                            int dim, int vdim, float scale, int window, int keep_first,
                                            const float* slopes, int sigmoid_weights, const float* head_bias,
                                            const float* sink, float out_scale, int* err_flag, int dtype, void* stream) {
+  return pg_attention_ragged_tc_masked(out, ld_out, q, ld_q, gate, ld_gate, gate_per_head, k_pool, ld_k, v_pool, ld_v, pool_rows,
+                                       page_table, pt_stride, page_size, tiles, n_tiles, n_tokens, n_heads, n_kv_heads, dim,
+                                       vdim, scale, window, keep_first, 0, slopes, sigmoid_weights, head_bias, sink, nullptr, 0,
+                                       out_scale, err_flag, dtype, stream);
+}
+
+extern "C" int pg_attention_ragged_tc_masked(void* out, int ld_out, const void* q, int ld_q, const void* gate, int ld_gate,
+                                             int gate_per_head, const void* k_pool, int ld_k, const void* v_pool, int ld_v,
+                                             long long pool_rows, const int32_t* page_table, int pt_stride, int page_size,
+                                             const int32_t* tiles, int n_tiles, int n_tokens, int n_heads, int n_kv_heads,
+                                             int dim, int vdim, float scale, int window, int keep_first, int chunk,
+                                             const float* slopes, int sigmoid_weights, const float* head_bias,
+                                             const float* sink, const float* out_rot, int out_rot_interleaved,
+                                             float out_scale, int* err_flag, int dtype, void* stream) {
   if (n_tiles <= 0) return PG_OK;
+  PG_REQUIRE(chunk >= 0 && (chunk == 0 || keep_first == 0), "attention_ragged_tc: blocks of %d positions with %d kept first ones",
+             chunk, keep_first);
   if (ld_k <= 0) ld_k = n_kv_heads * dim;
   if (ld_v <= 0) ld_v = n_kv_heads * vdim;
   PG_REQUIRE(ld_k >= n_kv_heads * dim && ld_v >= n_kv_heads * vdim && ld_k % 8 == 0 && ld_v % 8 == 0,
@@ -298,7 +361,7 @@ extern "C" int pg_attention_ragged_tc_sink(void* out, int ld_out, const void* q,
              "attention_ragged_tc: cuTensorMapEncodeTiled failed");
   tc::WinParams p = {out, ld_out, gate, ld_gate, tiles, page_table, pt_stride, n_heads, n_heads / n_kv_heads, dim, vdim,
                      scale, window, slopes, err_flag, keep_first, sigmoid_weights ? 1 : 0, head_bias,
-                     gate_per_head ? 1 : 0, out_scale, sink};
+                     gate_per_head ? 1 : 0, out_scale, sink, chunk, out_rot, out_rot_interleaved ? 1 : 0};
   const size_t smem = 1024 + (size_t)tc::WQ * dim * 2 + 2 * (size_t)tc::WK * dim * 2 + (size_t)tc::WK * vdim * 2 +
                       (size_t)tc::WQ * tc::WK * 2 + 72 + 16;
   cudaStream_t st = (cudaStream_t)stream;

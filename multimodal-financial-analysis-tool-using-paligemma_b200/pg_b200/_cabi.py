@@ -116,6 +116,8 @@ SIGNATURES = {
                                   _vp, _i, _i, _vp, _vp, _i, _i, _vp],
     "pg_attention_ragged_masked": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i,
                                    _i, _f, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _ll, _i, _vp],
+    "pg_attention_ragged_tc_masked": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i,
+                                      _i, _i, _f, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _vp],
     "pg_relu2": [_vp, _vp, _ll, _i, _vp],
     "pg_ssm_record_floats": [_i, _i, _i, _i],
     "pg_ssm_prep": [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],

@@ -92,13 +92,12 @@ def masked_softmax_attention(q, k, v, scale, visible, sink=None):
     n = q.shape[0]
     out = torch.zeros(n, v.shape[1], dtype=F64)
     for i in range(n):
-        js = [j for j in range(n) if visible(i, j)]
-        s = torch.stack([(q[i] * k[j]).sum() * scale for j in js])
+        js = torch.tensor([j for j in range(n) if visible(i, j)], dtype=torch.long)
+        s = (k[js] @ q[i]) * scale
         m = s.max() if sink is None else torch.maximum(s.max(), sink)
         e = torch.exp(s - m)
         den = e.sum() + (torch.exp(sink - m) if sink is not None else 0.0)
-        for w_, j in zip(e, js):
-            out[i] += (w_ / den) * v[j]
+        out[i] = (e / den) @ v[js]
     return out
 
 
@@ -204,3 +203,77 @@ def forward(cfg, W, tokens, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.clone())
     return lin(norm_one_plus(x, W["final.norm"], eps), W["head"]) * cfg.get("logit_scale", 1.0)
+
+
+# ------------------------------------------------------------------ configurations and random checkpoints for tests
+def latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, window, scale=None, base=10000.0):
+    return {"type": "latent_attention", "mixer": {
+        "heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+        "scale": scale if scale is not None else 1.0 / math.sqrt(dim + rot_dim), "mask": {"size": window},
+        "rot": {"dims": rot_dim, "base": base}}}
+
+
+def attention(heads, kv_heads, dim, vdim, chunk, rot_dims=None, factor=None, scale=None, base=10000.0):
+    rot = {"dims": dim if rot_dims is None else rot_dims, "base": base}
+    if factor is not None:
+        rot["scaling"] = {"factor": factor}
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+                                           "scale": scale if scale is not None else 1.0 / math.sqrt(dim),
+                                           "mask": {"size": chunk}, "rot": rot}}
+
+
+def mamba2(heads, vdim, state, groups, norm_groups, conv):
+    return {"type": "mamba2", "mixer": {"heads": heads, "vdim": vdim, "state": state, "groups": groups,
+                                        "norm_groups": norm_groups, "conv": conv}}
+
+
+def layer(mixer, ff):
+    return dict(mixer, mlp={"kind": "dense", "ff": ff} if ff else None)
+
+
+def make_config(width, vocab, layers, taps=4, eps=1e-5, logit_scale=1.0):
+    return {"architecture": "Gogivik", "vocab": vocab, "width": width, "norm": {"eps": eps}, "canon": {"taps": taps},
+            "logit_scale": logit_scale, "layers": layers}
+
+
+def make_checkpoint(cfg, seed=0, dtype=torch.bfloat16):
+    """Random weights rounded to `dtype` (so a 16-bit engine holds exactly the same numbers), returned as float32."""
+    g = torch.Generator().manual_seed(seed)
+    D, taps = cfg["width"], cfg["canon"]["taps"]
+
+    def mat(rows, cols, gain=1.0):
+        return (torch.randn(rows, cols, generator=g) * gain / math.sqrt(cols)).to(dtype).float()
+
+    def vec(n, mean=0.0, dev=0.2):
+        return (mean + dev * torch.randn(n, generator=g)).to(dtype).float()
+
+    W = {"embed": torch.randn(cfg["vocab"], D, generator=g).to(dtype).float(), "final.norm": vec(D),
+         "head": mat(cfg["vocab"], D, 2.0)}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        W[p + "norm1"] = vec(D)
+        W[p + "canon1"] = (torch.randn(D, taps, generator=g) * 0.4).to(dtype).float()
+        if L["type"] == "latent_attention":
+            H, d, r, e = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
+            W.update({p + "mix.dq": mat(m["q_rank"], D), p + "mix.dq.norm": vec(m["q_rank"], 1.0),
+                      p + "mix.uq": mat(H * (d + r), m["q_rank"], 2.5),
+                      p + "mix.dkv": mat(m["kv_rank"] + r, D, 2.0), p + "mix.dkv.norm": vec(m["kv_rank"], 1.0),
+                      p + "mix.uk": mat(H * d, m["kv_rank"], 2.5), p + "mix.uv": mat(H * e, m["kv_rank"], 1.5),
+                      p + "mix.sink": vec(H, 0.5, 1.0), p + "mix.o": mat(D, H * e)})
+        elif L["type"] == "attention":
+            H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            W.update({p + "mix.q": mat(H * d, D, 2.0), p + "mix.k": mat(G * d, D, 2.0), p + "mix.v": mat(G * e, D, 2.0),
+                      p + "mix.q.norm": vec(d, 1.5, 0.4), p + "mix.k.norm": vec(d, 1.5, 0.4), p + "mix.o": mat(D, H * e, 2.0)})
+        else:
+            H, e, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            ch = H * e + 2 * G * N
+            W.update({p + "mix.in": mat(2 * H * e + 2 * G * N + H, D, 2.0),
+                      p + "mix.conv": (torch.randn(ch, m["conv"], generator=g) * 0.5).to(dtype).float(),
+                      p + "mix.conv.b": vec(ch, 0.0, 0.3), p + "mix.dt_bias": vec(H, -1.0, 1.0),
+                      p + "mix.A_log": vec(H, -0.5, 1.0), p + "mix.D": vec(H, 1.0, 0.5), p + "mix.norm": vec(H * e, 1.0),
+                      p + "mix.o": mat(D, H * e, 1.5)})
+        if L.get("mlp"):
+            ff = L["mlp"]["ff"]
+            W.update({p + "norm2": vec(D), p + "canon2": (torch.randn(D, taps, generator=g) * 0.4).to(dtype).float(),
+                      p + "mlp.up": mat(ff, D, 2.0), p + "mlp.down": mat(D, ff)})
+    return W

@@ -1,0 +1,657 @@
+"""Gogivik on the GPU against the plain float64 oracle (tests/gogivik_oracle.py): every mechanism alone through the
+C ABI, then whole models of several shapes through the engine, its caches, its per-sequence state and the scheduler."""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+import gogivik_oracle as O
+from test_gpu_ninisun import Paged, _close, _i32, _rows_close, _tokens
+
+pytestmark = pytest.mark.gpu
+F64 = torch.float64
+PAGE = 64
+TOL = {torch.float32: 3e-5, torch.bfloat16: 5e-2}
+STRAY = {torch.float32: 0.0, torch.bfloat16: 0.02}
+CT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _lib():
+    from pg_b200 import _cabi as cabi
+    return cabi, cabi.lib(), cabi.stream()
+
+
+def _engine(cfg, seed=0, dtype=torch.float32, pool_tokens=1024, **kw):
+    from pg_b200.gogivik import GogivikEngine
+    ck = O.make_checkpoint(cfg, seed)
+    return GogivikEngine(cfg, ck, device="cuda:0", dtype=dtype, kv_pool_tokens=pool_tokens, **kw), ck
+
+
+def _segs(lens, slots):
+    segs, row = [], 0
+    for n, s in zip(lens, slots):
+        segs += [s, row, n]
+        row += n
+    return segs
+
+
+# ------------------------------------------------------------------ mechanisms alone (C ABI)
+@pytest.mark.parametrize("D", [48, 100, 1500])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_with_a_weight_stored_around_zero(D, dtype):
+    """x += y, then RMS(x) (1 + w) unrounded in fp32; the same through a row index into the model dtype."""
+    cabi, L, st = _lib()
+    g = torch.Generator().manual_seed(D)
+    T = 9
+    x0, y = torch.randn(T, D, generator=g) * 3, torch.randn(T, D + 4, generator=g).to(dtype)
+    w = (0.3 * torch.randn(D, generator=g)).to(dtype)
+    x, out = x0.clone().cuda(), torch.zeros(T, D, device="cuda")
+    yd, wd = y.cuda(), w.cuda()
+    cabi.check(L.pg_group_rmsnorm_ex(out.data_ptr(), x.data_ptr(), yd.data_ptr(), D + 4, None, 0, wd.data_ptr(), None, T, D, 1,
+                                     1e-3, 1, 1, CT[dtype], st))
+    s = x0.to(F64) + y[:, :D].to(F64)
+    _close(x, s, 1e-6)
+    _close(out, O.norm_one_plus(s, w.float(), 1e-3), 2e-6)
+    rows = [7, 0, 3]
+    picked = torch.zeros(3, D, dtype=dtype, device="cuda")
+    cabi.check(L.pg_group_rmsnorm_ex(picked.data_ptr(), x.data_ptr(), None, 0, None, 0, wd.data_ptr(), _i32(rows).data_ptr(), 3,
+                                     D, 1, 1e-3, 1, 0, CT[dtype], st))
+    _close(picked, O.norm_one_plus(x.cpu().to(F64)[rows], w.float(), 1e-3), 4e-3 if dtype == torch.bfloat16 else 2e-6)
+
+
+@pytest.mark.parametrize("taps,C", [(4, 40), (2, 7), (5, 300), (1, 16), (3, 1030)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_input_convolution_over_portions_slots_and_state(taps, C, dtype):
+    """Three sequences fed in portions of 1, 2 and more tokens side by side in changing order; every output equals the
+    convolution over the whole sequence, a slot that is not in a step keeps its state, a reused slot starts at zero."""
+    cabi, L, st = _lib()
+    g = torch.Generator().manual_seed(taps * 1000 + C)
+    lens = {"a": 23, "b": 9, "c": 14}
+    seq = {k: torch.randn(n, C, generator=g) for k, n in lens.items()}
+    w = (0.5 * torch.randn(C, taps, generator=g)).to(dtype)
+    want = {k: O.input_conv(v.to(F64), w.float()) for k, v in seq.items()}
+    slot = {"a": 2, "b": 0, "c": 2}                      # c takes over a's slot
+    state = torch.randn(3, max(taps - 1, 1), C, generator=g).cuda()      # garbage: a new sequence must not see it
+    wd = w.cuda()
+    plan = [[("a", 1), ("b", 2)], [("b", 1), ("a", 2)], [("a", 1)], [("a", 19), ("b", 5)], [("b", 1)], [("c", 2)], [("c", 1)],
+            [("c", 1)], [("c", 10)]]
+    fed = {k: 0 for k in lens}
+    got = {k: [] for k in lens}
+    for step in plan:
+        for k, _ in step:
+            if fed[k] == 0:
+                state[slot[k]].zero_()
+        rows = torch.cat([seq[k][fed[k]:fed[k] + n] for k, n in step]).cuda()
+        T = rows.shape[0]
+        out = torch.zeros(T, C, dtype=dtype, device="cuda")
+        slots = [slot[k] for k, n in step for _ in range(n)]
+        before = state.clone()
+        cabi.check(L.pg_time_conv_residual(out.data_ptr(), rows.data_ptr(), wd.data_ptr(), state.data_ptr(), _i32(slots).data_ptr(),
+                                           T, C, taps, CT[dtype], st))
+        segs = _segs([n for _, n in step], [slot[k] for k, _ in step]) + [1, 0, 0]
+        cabi.check(L.pg_time_conv_state(state.data_ptr(), rows.data_ptr(), C, 0, 1, _i32(segs).data_ptr(), len(segs) // 3, C,
+                                        taps, CT[dtype], st))
+        at = 0
+        for k, n in step:
+            got[k].append(out[at:at + n].float().cpu())
+            at += n
+            fed[k] += n
+        idle = [s for s in range(3) if s not in slots]
+        for s in idle:
+            assert torch.equal(state[s], before[s])
+    for k in lens:
+        _close(torch.cat(got[k]), want[k], 4e-3 if dtype == torch.bfloat16 else 2e-6)
+
+
+@pytest.mark.parametrize("H,G,dim,vdim,rot_dims,factor", [(4, 2, 12, 10, 8, 4.0), (3, 3, 16, 16, 16, None), (8, 1, 64, 32, 32, 2.0),
+                                                          (2, 1, 6, 2, 0, None), (16, 4, 128, 128, 128, 1.5)])
+def test_head_norms_rotation_of_keys_and_values_and_cache_append(H, G, dim, vdim, rot_dims, factor):
+    cabi, L, st = _lib()
+    from pg_b200.ragged_engine import RotaryCfg
+    g = torch.Generator().manual_seed(H * dim)
+    positions, slots = [70, 71, 0, 1, 63, 3000], [1, 1, 0, 0, 0, 2]
+    T = len(positions)
+    pg = Paged([64, 72, 3001], G * dim, G * vdim)
+    nq, nk, nv = H * dim, G * dim, G * vdim
+    ld = 3 + nq + 5 + nk + 1 + nv
+    q0, k0, v0 = 3, 3 + nq + 5, 3 + nq + 5 + nk + 1
+    proj = torch.randn(T, ld, generator=g) * 2
+    qw, kw = 1 + 0.5 * torch.randn(dim, generator=g), 1 + 0.5 * torch.randn(dim, generator=g)
+    sc = {"factor": factor} if factor else None
+    f64 = O.frequencies(rot_dims, 5000.0, factor or 1.0) if rot_dims else None
+    fv64 = O.frequencies(vdim, 5000.0)
+    freq = None
+    if rot_dims:
+        f_eng, mag = RotaryCfg(rot_dims, 5000.0, sc).table()
+        assert torch.allclose(f_eng, f64, rtol=1e-12) and mag == 1.0
+        freq = f_eng.float().cuda()
+    vfreq = RotaryCfg(vdim, 5000.0).table()[0].float().cuda()
+    q = torch.zeros(T, nq, device="cuda")
+    dev = [t.cuda() for t in (proj, qw, kw)]
+    cabi.check(L.pg_headnorm_rotary_append(q.data_ptr(), dev[0].data_ptr(), ld, q0, H, k0, G, dim, v0, vdim, dev[1].data_ptr(),
+                                           dev[2].data_ptr(), 1e-4, None if freq is None else freq.data_ptr(), rot_dims, 0, 1,
+                                           vfreq.data_ptr(), 0, pg.k.data_ptr(), pg.v.data_ptr(), pg.table.data_ptr(),
+                                           pg.max_pages, PAGE, _i32(slots).data_ptr(), _i32(positions).data_ptr(), T, 0, st))
+    p64 = proj.to(F64)
+    wq = O.rms(p64[:, q0:q0 + nq].view(T, H, dim), 1e-4) * qw.to(F64)
+    wk = O.rms(p64[:, k0:k0 + nk].view(T, G, dim), 1e-4) * kw.to(F64)
+    if rot_dims:
+        wq, wk = O.rotate(wq, positions, f64, "halves"), O.rotate(wk, positions, f64, "halves")
+    wv = O.rotate(O.rms(p64[:, v0:v0 + nv].view(T, G, vdim), 1e-4), positions, fv64, "halves")
+    rows = [pg.rows(s, [p])[0] for s, p in zip(slots, positions)]
+    _rows_close(q, wq.reshape(T, nq), 1e-4)            # fp32 angles: at position 3000 the product is some 1e-4 rad off
+    _rows_close(pg.k.view(-1, nk)[rows], wk.reshape(T, nk), 1e-4)
+    _rows_close(pg.v.view(-1, nv)[rows], wv.reshape(T, nv), 1e-4)
+    _rows_close(q[:5], wq.reshape(T, nq)[:5], 3e-6)
+    untouched = torch.ones(pg.k.shape[0] * PAGE, dtype=torch.bool)
+    untouched[rows] = False
+    assert bool((pg.k.view(-1, nk).cpu()[untouched] == 7.0).all()) and bool((pg.v.view(-1, nv).cpu()[untouched] == -9.0).all())
+
+
+def _block_attention_case(H, G, dim, vdim, chunk, lens, new, dtype=torch.float32, tower=None, seed=0, tc=False, window=0,
+                          interleaved=False):
+    """Sequences of lens[s] cached tokens of which the last new[s] are this step's queries.  The cached values are
+    rotated by their positions; the kernel has to turn its result back.  Returns (got, want)."""
+    cabi, L, st = _lib()
+    g = torch.Generator().manual_seed(seed)
+    pg = Paged(lens, G * dim, G * vdim, dtype)
+    scale = 0.4
+    fv = O.frequencies(vdim, 300.0)
+    layout = "neighbours" if interleaved else "halves"
+    qs, want, slots, positions = [], [], [], []
+    for s, (n, m) in enumerate(zip(lens, new)):
+        q, k, v = torch.randn(n, H, dim, generator=g), torch.randn(n, G, dim, generator=g), torch.randn(n, G, vdim, generator=g)
+        if tower is not None:                     # one key whose score stands far out for the last query
+            j = tower(n - 1)
+            if 0 <= j < n:
+                k[j] = 12.0 * q[n - 1, ::H // G] / scale / dim
+                v[j] += 50.0
+        v = O.rotate(v.to(F64), list(range(n)), fv, layout).float()
+        if dtype != torch.float32:
+            q, k, v = (t.to(dtype).float() for t in (q, k, v))
+        pg.fill(s, k, v)
+        outs = []
+        for h in range(H):
+            gi = h // (H // G)
+            vis = (lambda i, j: O.chunk_visible(i, j, chunk) if chunk else j <= i)
+            vis2 = (lambda i, j: vis(i, j) and (window <= 0 or i - j < window))
+            o = O.masked_softmax_attention(q[:, h].to(F64), k[:, gi].to(F64), v[:, gi].to(F64), scale, vis2)
+            outs.append(O.rotate(o, list(range(n)), fv, layout, sign=-1.0))
+        o = torch.stack(outs, 1)
+        qs.append(q[n - m:].reshape(m, H * dim))
+        want.append(o[n - m:].reshape(m, H * vdim))
+        slots += [s] * m
+        positions += list(range(n - m, n))
+    q_all = torch.cat(qs).to(dtype).cuda()
+    T = q_all.shape[0]
+    out = torch.zeros(T, H * vdim + 8, dtype=dtype, device="cuda")
+    fvd = fv.float().cuda()
+    if tc:
+        tiles, t0 = [], 0
+        while t0 < T:
+            t1 = t0 + 1
+            while t1 < T and t1 - t0 < 128 and slots[t1] == slots[t0]:
+                t1 += 1
+            tiles += [t0, t1 - t0, slots[t0], positions[t0]]
+            t0 = t1
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        cabi.check(L.pg_attention_ragged_tc_masked(
+            out.data_ptr(), H * vdim + 8, q_all.data_ptr(), H * dim, None, 0, 0, pg.k.data_ptr(), 0, pg.v.data_ptr(), 0,
+            pg.k.shape[0] * PAGE, pg.table.data_ptr(), pg.max_pages, PAGE, _i32(tiles).data_ptr(), len(tiles) // 4, T, H, G,
+            dim, vdim, scale, window, 0, chunk, None, 0, None, None, fvd.data_ptr(), 1 if interleaved else 0, 1.0,
+            err.data_ptr(), CT[dtype], st))
+        torch.cuda.synchronize()
+        assert int(err) == 0
+    else:
+        ws = torch.empty(1 << 20, device="cuda")
+        cabi.check(L.pg_attention_ragged_masked(
+            out.data_ptr(), H * vdim + 8, q_all.data_ptr(), H * dim, None, 0, 0, pg.k.data_ptr(), 0, pg.v.data_ptr(), 0,
+            pg.table.data_ptr(), pg.max_pages, PAGE, _i32(slots).data_ptr(), _i32(positions).data_ptr(), T, H, G, dim, vdim,
+            scale, window, 0, chunk, None, 0, None, None, fvd.data_ptr(), 1 if interleaved else 0, 1.0, ws.data_ptr(),
+            ws.numel(), CT[dtype], st))
+        torch.cuda.synchronize()
+    return out[:, :H * vdim].float(), torch.cat(want)
+
+
+@pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 8, 16), (6, 1, 12, 20), (2, 2, 48, 48), (8, 2, 32, 34), (4, 1, 16, 128), (2, 1, 24, 6)])
+@pytest.mark.parametrize("chunk", [0, 1, 5, 64, 75, 200])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_block_masked_attention_turns_rotated_values_back(H, G, dim, vdim, chunk, interleaved):
+    """Prompt portions and single decoded tokens in one launch: positions at, before and after block borders."""
+    got, want = _block_attention_case(H, G, dim, vdim, chunk, lens=[150, 76, 1, 65, 129], new=[150, 1, 1, 3, 2],
+                                      interleaved=interleaved)
+    _rows_close(got, want, 2e-5)
+
+
+@pytest.mark.parametrize("chunk", [7, 64, 96])
+@pytest.mark.parametrize("where", ["block_start", "before_block", "two_before", "first", "self"])
+@pytest.mark.parametrize("decode", [False, True])
+def test_a_towering_key_at_every_block_edge(chunk, where, decode):
+    """One key that would take all the weight sits at the first position of the query's block (seen), right before it
+    or two before it (not seen), at position 0 or at the query itself; the query is the last token of 3 blocks + 2."""
+    n = 3 * chunk + 3
+    last = n - 1
+    j = {"block_start": last // chunk * chunk, "before_block": last // chunk * chunk - 1,
+         "two_before": last // chunk * chunk - 2, "first": 0, "self": last}[where]
+    got, want = _block_attention_case(2, 1, 16, 16, chunk, lens=[n], new=[1 if decode else n], tower=lambda _: j)
+    seen = where in ("block_start", "self")
+    assert (float(want[-1].abs().max()) > 20.0) == seen      # the oracle itself tells the two cases apart
+    _rows_close(got, want, 2e-5)
+
+
+@pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 64, 64), (2, 1, 128, 64), (3, 3, 64, 128)])
+@pytest.mark.parametrize("chunk", [0, 40, 64, 96, 300])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_tensor_core_block_masked_attention(H, G, dim, vdim, chunk, interleaved):
+    """Prompt portions (tiles of up to 128 rows that start anywhere in a block) through the tcgen05 kernel."""
+    got, want = _block_attention_case(H, G, dim, vdim, chunk, lens=[300, 190, 77], new=[300, 131, 50], dtype=torch.bfloat16,
+                                      tc=True, interleaved=interleaved)
+    _rows_close(got, want, 3e-2)
+
+
+@pytest.mark.parametrize("chunk", [64, 96, 100])
+@pytest.mark.parametrize("where", ["block_start", "before_block", "first", "self"])
+def test_tensor_core_towering_key_at_every_block_edge(chunk, where):
+    n = 3 * chunk + 3
+    last = n - 1
+    j = {"block_start": last // chunk * chunk, "before_block": last // chunk * chunk - 1, "first": 0, "self": last}[where]
+    got, want = _block_attention_case(2, 1, 64, 64, chunk, lens=[n], new=[n], dtype=torch.bfloat16, tower=lambda _: j, tc=True)
+    assert (float(want[-1].abs().max()) > 20.0) == (where in ("block_start", "self"))
+    _rows_close(got, want, 3e-2)
+
+
+def test_squared_relu():
+    cabi, L, st = _lib()
+    for dtype, n in ((torch.float32, 1003), (torch.bfloat16, 4096)):
+        z = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(dtype).cuda()
+        out = torch.empty_like(z)
+        cabi.check(L.pg_relu2(out.data_ptr(), z.data_ptr(), n, CT[dtype], st))
+        _close(out, torch.relu(z.cpu().to(F64)) ** 2, 4e-3 if dtype == torch.bfloat16 else 1e-7)
+
+
+@pytest.mark.parametrize("H,e,N,G,ng,taps", [(4, 6, 8, 2, 1, 3), (6, 32, 32, 2, 2, 4), (3, 7, 5, 3, 3, 2), (2, 64, 128, 1, 1, 4),
+                                             (5, 12, 130, 1, 5, 1), (8, 16, 64, 8, 4, 5)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_state_space_mixer_over_portions_and_slots(H, e, N, G, ng, taps, dtype):
+    """Convolution + silu, step sizes, decays, the scan and the gated group norm of two sequences fed in portions side
+    by side (one of them into a slot whose state another sequence left) against the oracle over whole sequences."""
+    cabi, L, st = _lib()
+    g = torch.Generator().manual_seed(H * 100 + N)
+    inner, ch = H * e, H * e + 2 * G * N
+    ld = 2 * inner + 2 * G * N + H
+    lens = {"a": 37, "b": 12}
+    proj = {k: (torch.randn(n, ld, generator=g) * 1.5).to(dtype) for k, n in lens.items()}
+    W = {"conv": (0.5 * torch.randn(ch, taps, generator=g)).to(dtype).float(), "conv.b": (0.3 * torch.randn(ch, generator=g)).to(dtype).float(),
+         "dt_bias": torch.randn(H, generator=g) - 1.0, "A_log": torch.randn(H, generator=g) - 0.5, "D": torch.randn(H, generator=g),
+         "norm": (1 + 0.3 * torch.randn(inner, generator=g)).to(dtype).float()}
+    want = {}
+    for k, pr in proj.items():
+        u, n = pr.to(F64), lens[k]
+        xbc = O.silu(O.causal_conv(u[:, inner:inner + ch], W["conv"], W["conv.b"]))
+        dt = O.softplus(u[:, inner + ch:] + W["dt_bias"].to(F64))
+        y = O.selective_scan(xbc[:, :inner].reshape(n, H, e), xbc[:, inner:inner + G * N].reshape(n, G, N),
+                             xbc[:, inner + G * N:].reshape(n, G, N), dt, W["A_log"].to(F64), W["D"].to(F64), H // G).reshape(n, inner)
+        y = y * O.silu(u[:, :inner])
+        want[k] = O.rms(y.view(n, ng, inner // ng), 1e-5).reshape(n, inner) * W["norm"].to(F64)
+    slot = {"a": 1, "b": 0}
+    S = torch.randn(2, H, N, e, generator=g).cuda()
+    cs = torch.randn(2, max(taps - 1, 1), ch, generator=g).cuda()
+    S.zero_()
+    cs.zero_()
+    dev = {k: (v.to(dtype) if k in ("conv", "conv.b", "norm") else v).cuda() for k, v in W.items()}
+    plan = [[("a", 2), ("b", 1)], [("b", 1), ("a", 1)], [("a", 30), ("b", 2)], [("b", 8), ("a", 1)], [("a", 3)]]
+    fed = {k: 0 for k in lens}
+    got = {k: [] for k in lens}
+    for step in plan:
+        rows = torch.cat([proj[k][fed[k]:fed[k] + n] for k, n in step]).cuda()
+        T = rows.shape[0]
+        slots = [slot[k] for k, n in step for _ in range(n)]
+        segs = _i32(_segs([n for _, n in step], [slot[k] for k, _ in step]) + [0, 0, 0])
+        rec = torch.empty(L.pg_ssm_record_floats(T, H, e, N), device="cuda")
+        cabi.check(L.pg_ssm_prep(rec.data_ptr(), rows.data_ptr(), ld, inner, inner + ch, dev["conv"].data_ptr(), dev["conv.b"].data_ptr(),
+                                 cs.data_ptr(), dev["dt_bias"].data_ptr(), dev["A_log"].data_ptr(), _i32(slots).data_ptr(), T, H, e,
+                                 N, G, taps, CT[dtype], st))
+        cabi.check(L.pg_time_conv_state(cs.data_ptr(), rows.data_ptr(), ld, inner, 0, segs.data_ptr(), len(step) + 1, ch, taps,
+                                        CT[dtype], st))
+        y = torch.zeros(T, inner, device="cuda")
+        cabi.check(L.pg_lightning_attention_ex(y.data_ptr(), S.data_ptr(), rec.data_ptr(), None, dev["D"].data_ptr(), segs.data_ptr(),
+                                               len(step) + 1, H, N, e, st))
+        out = torch.zeros(T, inner, dtype=dtype, device="cuda")
+        cabi.check(L.pg_gate_groupnorm(out.data_ptr(), inner, y.data_ptr(), rows.data_ptr(), ld, dev["norm"].data_ptr(), T, inner,
+                                       ng, 1e-5, CT[dtype], st))
+        at = 0
+        for k, n in step:
+            got[k].append(out[at:at + n].float().cpu())
+            at += n
+            fed[k] += n
+    for k in lens:
+        assert fed[k] == lens[k]
+        _rows_close(torch.cat(got[k]), want[k], 6e-3 if dtype == torch.bfloat16 else 3e-5)
+
+
+def test_state_space_state_carries_a_first_token_far():
+    """A decay of (almost) 1: what the first token wrote is read 400 tokens later, whole or cut into portions."""
+    cabi, L, st = _lib()
+    H, e, N, G, taps, T = 1, 8, 8, 1, 2, 401
+    inner, ch = H * e, H * e + 2 * N
+    ld = 2 * inner + 2 * N + H
+    proj = torch.zeros(T, ld)
+    proj[0, inner:inner + ch] = 6.0                      # x, B of the first token (C too, unused there)
+    proj[T - 1, inner + e + N:inner + ch] = 6.0          # the last token asks with its C
+    proj[:, inner + ch:] = 2.0                           # dt
+    conv = torch.zeros(ch, taps)
+    conv[:, -1] = 1.0
+    W = dict(conv=conv, b=torch.zeros(ch), dt_bias=torch.zeros(H), A_log=torch.full((H,), -30.0), D=torch.zeros(H))
+    xbc = O.silu(O.causal_conv(proj[:, inner:inner + ch].to(F64), conv, W["b"]))
+    dt = O.softplus(proj[:, inner + ch:].to(F64))
+    want = O.selective_scan(xbc[:, :inner].reshape(T, H, e), xbc[:, inner:inner + N].reshape(T, G, N), xbc[:, inner + N:].reshape(T, G, N),
+                            dt, W["A_log"].to(F64), W["D"].to(F64), 1).reshape(T, inner)
+    assert float(want[T - 1].abs().min()) > 100
+    dev = {k: v.cuda() for k, v in W.items()}
+    projd = proj.cuda()
+    for cuts in ([T], [1, 2, 61, 64, 200, 2, 1, 69, 1]):
+        assert sum(cuts) == T
+        S, cs = torch.zeros(1, H, N, e, device="cuda"), torch.zeros(1, taps - 1, ch, device="cuda")
+        out = torch.zeros(T, inner, device="cuda")
+        at = 0
+        for n in cuts:
+            rec = torch.empty(L.pg_ssm_record_floats(n, H, e, N), device="cuda")
+            rows = projd[at:at + n]
+            segs = _i32([0, 0, n])
+            cabi.check(L.pg_ssm_prep(rec.data_ptr(), rows.data_ptr(), ld, inner, inner + ch, dev["conv"].data_ptr(), dev["b"].data_ptr(),
+                                     cs.data_ptr(), dev["dt_bias"].data_ptr(), dev["A_log"].data_ptr(), _i32([0] * n).data_ptr(), n,
+                                     H, e, N, G, taps, 0, st))
+            cabi.check(L.pg_time_conv_state(cs.data_ptr(), rows.data_ptr(), ld, inner, 0, segs.data_ptr(), 1, ch, taps, 0, st))
+            cabi.check(L.pg_lightning_attention_ex(out[at:].data_ptr(), S.data_ptr(), rec.data_ptr(), None, dev["D"].data_ptr(),
+                                                   segs.data_ptr(), 1, H, N, e, st))
+            at += n
+        _close(out, want, 1e-5)
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 72, 130])
+@pytest.mark.parametrize("where", ["edge_in", "edge_out", "first", "self"])
+@pytest.mark.parametrize("decode", [False, True])
+def test_latent_space_window_edges_with_a_sink(window, where, decode):
+    """The kernel the latent mixer runs on (one key/value head, values a prefix of the key rows, a sink per head): a
+    towering key at the last position the window keeps, at the first it has dropped, at position 0 and at the query."""
+    cabi, L, st = _lib()
+    H, kvr, rot = 3, 24, 8
+    ldq, ldp = kvr + rot, 32
+    n = 2 * window + 70
+    last = n - 1
+    j = {"edge_in": last - window + 1, "edge_out": last - window, "first": 0, "self": last}[where]
+    g = torch.Generator().manual_seed(window)
+    scale = 0.3
+    q, kx = torch.randn(n, H, ldq, generator=g), torch.randn(n, ldq, generator=g)
+    kx[j] = 12.0 * q[last, 0] / scale / ldq
+    kx[j, :kvr] += 20.0 * torch.sign(kx[j, :kvr])
+    q[last, 1:] = q[last, 0]
+    sink = torch.tensor([0.5, -1.0, 2.0])
+    pg = Paged([n], ldp, 1)
+    pg.fill(0, torch.cat([kx, torch.zeros(n, ldp - ldq)], -1), torch.zeros(n, 1))
+    want = torch.stack([O.masked_softmax_attention(q[:, h].to(F64), kx.to(F64), kx[:, :kvr].to(F64), scale,
+                                                   lambda i, jj: O.window_visible(i, jj, window), sink=sink.to(F64)[h])
+                        for h in range(H)], 1)
+    m = 1 if decode else n
+    qd = q[n - m:].reshape(m, H * ldq).cuda()
+    out = torch.zeros(m, H * kvr, device="cuda")
+    ws = torch.empty(1 << 20, device="cuda")
+    cabi.check(L.pg_attention_ragged_sink(out.data_ptr(), H * kvr, qd.data_ptr(), H * ldq, None, 0, 0, pg.k.data_ptr(), ldp,
+                                          pg.k.data_ptr(), ldp, pg.table.data_ptr(), pg.max_pages, PAGE, _i32([0] * m).data_ptr(),
+                                          _i32(list(range(n - m, n))).data_ptr(), m, H, 1, ldq, kvr, scale, window, 0, None, 0,
+                                          None, sink.cuda().data_ptr(), 1.0, ws.data_ptr(), ws.numel(), 0, st))
+    seen = where in ("edge_in", "self") or (where == "first" and window >= n)
+    assert (float(want[-1].abs().max()) > 15.0) == seen
+    _rows_close(out, want[n - m:].reshape(m, H * kvr), 2e-5)
+
+
+# ------------------------------------------------------------------ whole models
+CONFIGS = {
+    # every kind of layer, a layer without a feed-forward, windows and blocks of a few tokens so that every edge is crossed
+    # many times, grouped key/value heads, part of the head rotated, scaled frequencies
+    "small": O.make_config(width=48, vocab=61, taps=3, logit_scale=1.5, layers=[
+        O.layer(O.latent(heads=3, dim=8, rot_dim=4, vdim=6, q_rank=10, kv_rank=12, window=9), 40),
+        O.layer(O.attention(heads=4, kv_heads=2, dim=12, vdim=10, chunk=7, rot_dims=8, factor=4.0), 0),
+        O.layer(O.mamba2(heads=4, vdim=6, state=8, groups=2, norm_groups=1, conv=3), 24),
+        O.layer(O.attention(heads=2, kv_heads=2, dim=8, vdim=8, chunk=64), 16),
+        O.layer(O.latent(heads=2, dim=6, rot_dim=2, vdim=8, q_rank=8, kv_rank=8, window=70), 0)]),
+    # values the other configurations make equal or 1: one head, one group per head, a window and a block of one
+    # position, taps of 2 and 5, one tap in the mixer's own convolution, state-space layers first and last
+    "odd": O.make_config(width=52, vocab=67, taps=5, eps=1e-3, logit_scale=0.5, layers=[
+        O.layer(O.mamba2(heads=5, vdim=4, state=6, groups=5, norm_groups=5, conv=2), 0),
+        O.layer(O.attention(heads=5, kv_heads=1, dim=6, vdim=14, chunk=1, rot_dims=2), 28),
+        O.layer(O.latent(heads=1, dim=10, rot_dim=6, vdim=5, q_rank=7, kv_rank=9, window=1), 12),
+        O.layer(O.attention(heads=1, kv_heads=1, dim=20, vdim=6, chunk=33, factor=1.0), 0),
+        O.layer(O.mamba2(heads=1, vdim=12, state=20, groups=1, norm_groups=3, conv=1), 20)]),
+    # head sizes of real models: the 16-bit run crosses the tensor-core attention (blocks, turned-back values, the
+    # latent window) and the tensor-core GEMMs
+    "wide": O.make_config(width=256, vocab=300, taps=4, layers=[
+        O.layer(O.attention(heads=4, kv_heads=2, dim=64, vdim=64, chunk=96, factor=2.0), 256),
+        O.layer(O.latent(heads=4, dim=32, rot_dim=64, vdim=32, q_rank=64, kv_rank=64, window=72, scale=0.1), 128),
+        O.layer(O.mamba2(heads=4, vdim=64, state=128, groups=2, norm_groups=2, conv=4), 128),
+        O.layer(O.attention(heads=2, kv_heads=1, dim=128, vdim=64, chunk=50, rot_dims=64), 0)]),
+}
+_ORACLE_CACHE = {}
+
+
+def _stray(name, dtype):
+    """16-bit runs: rows that may differ.  The sizes of "odd" (norms over 4 to 6 numbers, one head, a block of one
+    position) make single rows a matter of rounding."""
+    return 0.06 if (name == "odd" and dtype == torch.bfloat16) else STRAY[dtype]
+
+
+def _oracle(name, n, seed=0):
+    key = (name, n, seed)
+    if key not in _ORACLE_CACHE:
+        cfg = CONFIGS[name]
+        ck = O.make_checkpoint(cfg, 0)
+        toks = _tokens(n, cfg["vocab"], 100 + seed)
+        sink = []
+        _ORACLE_CACHE[key] = (toks, O.forward(cfg, ck, toks, sink), sink)
+    return _ORACLE_CACHE[key]
+
+
+def test_taps_of_two():
+    cfg = O.make_config(width=32, vocab=40, taps=2, layers=[O.layer(O.mamba2(heads=2, vdim=8, state=4, groups=1, norm_groups=2, conv=4), 16),
+                                                            O.layer(O.attention(heads=2, kv_heads=1, dim=8, vdim=8, chunk=3), 16)])
+    ck = O.make_checkpoint(cfg, 1)
+    toks = _tokens(30, 40, 5)
+    eng, _ = _engine(cfg, seed=1)
+    b = eng.new_batcher(slots=1)
+    b.admit("a")
+    got = [b.run_entries([("a", toks[:11], list(range(11)))])] + [b.run_entries([("a", [t], [0])]) for t in toks[11:]]
+    _rows_close(torch.cat(got), O.forward(cfg, ck, toks), 1e-4)
+    b.close()
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_whole_prompt_logits_and_every_layer(name, dtype):
+    n = 150
+    toks, want, layers = _oracle(name, n)
+    eng, _ = _engine(CONFIGS[name], dtype=dtype)
+    b = eng.new_batcher(slots=2)
+    b.admit("a")
+    sink = []
+    got = b.run_entries([("a", toks, list(range(n)))], layer_sink=sink)
+    eng.check_errors(sync=True)
+    assert len(sink) == len(layers) == len(CONFIGS[name]["layers"])
+    for x, ref in zip(sink, layers):
+        _rows_close(x, ref, TOL[dtype], _stray(name, dtype))
+    _rows_close(got, want, TOL[dtype] * 2, _stray(name, dtype))
+    b.close()
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prefill_then_token_by_token_and_portions(name, dtype):
+    n = 150
+    toks, want, _ = _oracle(name, n)
+    eng, _ = _engine(CONFIGS[name], dtype=dtype, pool_tokens=448)
+    b = eng.new_batcher(slots=2)
+    b.admit("a")
+    rows = [b.run_entries([("a", toks[:100], [99])])]
+    rows += [b.run_entries([("a", [t], [0])]) for t in toks[100:]]
+    _rows_close(torch.cat(rows), want[99:], TOL[dtype] * 2, _stray(name, dtype))
+    b.finish("a")
+    b.admit("b")          # the slot, the state and the pages of "a" again; portions down to two tokens and single ones
+    at, got = 0, []
+    for size in [2, 37, 2, 1, 31, 13, 1, 1, 2, 50, 3, 7]:
+        got.append(b.run_entries([("b", toks[at:at + size], list(range(size)))]))
+        at += size
+    assert at == n
+    _rows_close(torch.cat(got), want, TOL[dtype] * 2, _stray(name, dtype))
+    eng.check_errors(sync=True)
+    b.close()
+
+
+@pytest.mark.parametrize("name,dtype", [("small", torch.float32), ("odd", torch.float32), ("wide", torch.float32),
+                                        ("wide", torch.bfloat16)])
+def test_unequal_requests_in_one_batch_with_slots_and_pages_used_again(name, dtype):
+    cfg = CONFIGS[name]
+    lens = {"a": 131, "b": 23, "c": 97, "d": 150, "e": 70}
+    ref = {k: _oracle(name, n, seed=i) for i, (k, n) in enumerate(lens.items())}
+    eng, _ = _engine(cfg, dtype=dtype, pool_tokens=6 * PAGE)          # a pool that forces pages to be handed on
+    b = eng.new_batcher(slots=3)
+    fed = {k: 0 for k in lens}
+    got = {k: [] for k in lens}
+    plan = [
+        [("a", 64), ("b", 21), ("c", 2)], [("a", 3), ("b", 1), ("c", 90)], [("a", 1), ("b", 1), ("c", 1)],
+        [("a", 60), ("c", 1)], [("c", 1), ("a", 1)], [("c", 2)], [("a", 2), ("d", 65)], [("d", 2), ("e", 64)],
+        [("d", 80), ("e", 1)], [("e", 5), ("d", 1)], [("d", 2)]]
+    for step in plan:
+        entries = []
+        for k, n in step:
+            if k not in b.slot_of:
+                b.admit(k)
+            entries.append((k, ref[k][0][fed[k]:fed[k] + n], list(range(n))))
+            fed[k] += n
+        out = b.run_entries(entries)
+        at = 0
+        for k, n in step:
+            got[k].append(out[at:at + n])
+            at += n
+        for k, _ in step:
+            if fed[k] == lens[k] and k in b.slot_of:
+                b.finish(k)
+    eng.check_errors(sync=True)
+    for k in lens:
+        assert fed[k] == lens[k]
+        _rows_close(torch.cat(got[k]), ref[k][1], TOL[dtype] * 2, STRAY[dtype])
+    b.close()
+    assert eng.pages_in_use() == 0
+
+
+def test_long_decoding_through_windows_blocks_pages_and_state():
+    name, n = "small", 330
+    toks, want, _ = _oracle(name, n)
+    for dtype in (torch.float32, torch.bfloat16):
+        eng, _ = _engine(CONFIGS[name], dtype=dtype)
+        b = eng.new_batcher(slots=1)
+        b.admit("a")
+        rows = [b.run_entries([("a", toks[:5], list(range(5)))])]
+        rows += [b.run_entries([("a", [t], [0])]) for t in toks[5:]]
+        _rows_close(torch.cat(rows), want, TOL[dtype] * 2, STRAY[dtype])
+        b.close()
+
+
+def test_state_of_every_sublayer_and_a_slot_handed_on():
+    cfg = CONFIGS["small"]
+    eng, _ = _engine(cfg)
+    assert sorted(eng.c_pools) == [0, 4] and sorted(eng.k_pools) == [1, 3]
+    b = eng.new_batcher(slots=2)
+    s = b.kv.state.layers
+    assert s[("canon1", 1)].shape == (2, 2, 48) and ("canon2", 1) not in s and s[("canon2", 0)].shape == (2, 2, 48)
+    assert s[("ssm", 2)].shape == (2, 4, 8, 6) and s[("conv", 2)].shape == (2, 2, 4 * 6 + 2 * 2 * 8)
+    b.admit("a")
+    b.run_entries([("a", _tokens(70, 61, 1), [])])
+    assert all(float(t[0].abs().max()) > 0 and float(t[1].abs().max()) == 0 for t in s.values())
+    b.finish("a")
+    b.admit("again")                                              # the slot is handed on with a zero state
+    assert all(float(t[0].abs().max()) == 0 for t in s.values())
+    b.close()
+
+
+def test_greedy_generation_through_the_scheduler():
+    cfg = CONFIGS["small"]
+    ck = O.make_checkpoint(cfg, 0)
+    eng, _ = _engine(cfg)
+    prompts = [_tokens(n, cfg["vocab"], 40 + n) for n in (3, 70, 18)]
+    b = eng.new_batcher(slots=2, token_budget=32)
+    rids = [b.submit(p, max_new_tokens=6) for p in prompts]
+    done = b.run()
+    for rid, p in zip(rids, prompts):
+        seq = list(p)
+        for _ in range(6):                                     # the oracle's own greedy loop
+            seq.append(int(O.forward(cfg, ck, seq)[-1].argmax()))
+        assert done[rid].tokens == seq[len(p):]
+    b.close()
+    assert eng.pages_in_use() == 0
+    runs = []
+    for _ in range(2):
+        b = eng.new_batcher(slots=2, token_budget=32, do_sample=True, temperature=0.9, top_p=0.8, seed=5)
+        rids = [b.submit(p, max_new_tokens=5) for p in prompts[:2]]
+        done = b.run()
+        runs.append([done[r].tokens for r in rids])
+        b.close()
+    assert runs[0] == runs[1] and all(0 <= t < cfg["vocab"] for seq in runs[0] for t in seq)
+
+
+def test_model_folder_through_the_registry_and_command_line(tmp_path):
+    import subprocess
+    import sys
+    import numpy as np
+    from pg_b200.checkpoint import write_safetensors
+    from pg_b200.registry import load_engine
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = CONFIGS["odd"]
+    ck = O.make_checkpoint(cfg, 3)
+    model = tmp_path / "model"
+    model.mkdir()
+    with open(model / "config.json", "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(str(model / "model.safetensors"), {k: v.to(torch.bfloat16) for k, v in ck.items()})
+    eng = load_engine(str(model), device="cuda:0", dtype=torch.float32, kv_pool_tokens=256)
+    assert type(eng).__name__ == "GogivikEngine"
+    toks = _tokens(40, cfg["vocab"], 9)
+    b = eng.new_batcher(slots=1)
+    b.admit(0)
+    _rows_close(b.run_entries([(0, toks, [39, 0])]), O.forward(cfg, ck, toks)[[39, 0]], 1e-4)
+    b.close()
+    more = dict(ck)
+    more["l0.mix.extra"] = torch.zeros(3)
+    with pytest.warns(UserWarning):
+        type(eng)(cfg, more, device="cuda:0", dtype=torch.float32, kv_pool_tokens=64)
+    with pytest.raises(ValueError):
+        type(eng)(cfg, more, device="cuda:0", dtype=torch.float32, kv_pool_tokens=64, strict=True)
+    with pytest.raises(KeyError):
+        type(eng)(cfg, {k: v for k, v in ck.items() if k != "l2.mix.sink"}, device="cuda:0", dtype=torch.float32, kv_pool_tokens=64)
+    seq = {k: _tokens(n, cfg["vocab"], 60 + n) for k, n in (("a", 22), ("b", 5), ("c", 70))}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": seq["a"][:20], "want": [19]}, {"id": "b", "tokens": seq["b"], "want": [0, 4]}],
+         "end": ["b"]},
+        {"step": 1, "entries": [{"id": "a", "tokens": seq["a"][20:21], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "c", "tokens": seq["c"], "want": [69]}, {"id": "a", "tokens": seq["a"][21:], "want": [0]}],
+         "end": ["a", "c"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model), "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [ln for ln in r.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2"]
+    ref = {k: O.forward(cfg, ck, v) for k, v in seq.items()}
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(3, cfg["vocab"]))
+    _rows_close(got0, torch.stack([ref["a"][19], ref["b"][0], ref["b"][4]]), 1e-4)
+    got2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, cfg["vocab"]))
+    _rows_close(got2, torch.stack([ref["c"][69], ref["a"][21]]), 1e-4)
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "generate"), "--model", str(model), "--dtype", "float32",
+                        "--prompt-ids", ",".join(map(str, seq["b"])), "--max-new-tokens", "4", "--max-tokens", "256",
+                        "--slots", "2"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(ln) for ln in r.stdout.splitlines() if ln.startswith("{")]
+    s = list(seq["b"])
+    for _ in range(4):
+        s.append(int(O.forward(cfg, ck, s)[-1].argmax()))
+    assert lines[0] == {"request": 0, "tokens": s[len(seq["b"]):]}
