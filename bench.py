@@ -660,7 +660,7 @@ def run_ours(args, rank, world, local):
 
 
 def run_arch(args):
-    """`--arch mubasun | ninisun | birizen`: see pg_b200/arch_bench.py.  One JSON line; `value` is the prefill throughput at the
+    """`--arch mubasun | ninisun | birizen | gogivik`: see pg_b200/arch_bench.py.  One JSON line; `value` is the prefill throughput at the
     largest size, the rest (decode, per-op rooflines, the numbers of the closest existing model at equal size) rides
     along."""
     from pg_b200 import arch_bench
@@ -668,7 +668,8 @@ def run_arch(args):
     pk = measured_peaks()
     sizes = [x for x in args.arch_sizes.split(",") if x]
     with ClockSampler(0) as clk:
-        runner = {"ninisun": arch_bench.run_ninisun, "birizen": arch_bench.run_birizen}.get(args.arch, arch_bench.run)
+        runner = {"ninisun": arch_bench.run_ninisun, "birizen": arch_bench.run_birizen,
+                  "gogivik": arch_bench.run_gogivik}.get(args.arch, arch_bench.run)
         res = runner(sizes, steps=min(args.steps, 16), warmup=args.warmup, peaks=pk)
     head = res[sizes[-1]]
     emit({"metric": f"{args.arch}_prefill_tokens_per_s", "value": head["prefill"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
@@ -715,10 +716,11 @@ def main():
                     help="N > 1: what `value` measures. tp = ONE sequence, tensor-parallel decoder (strong scaling, the north "
                          "star's sharding); replicas = one independent sequence per GPU (weak scaling, no data-path "
                          "collective).  Both are measured in every N > 1 run; the other one is reported beside the headline.")
-    ap.add_argument("--arch", default=None, choices=["mubasun", "ninisun", "birizen"],
+    ap.add_argument("--arch", default=None, choices=["mubasun", "ninisun", "birizen", "gogivik"],
                     help="instead of the default workload: prefill / decode throughput of this decoder-only design at "
                          "real-model layer sizes (random weights) beside the closest existing model at equal size (the "
-                         "Gemma decoder for mubasun, a dense Mubasun for ninisun, the MoE Mubasun and Ninisun for birizen), "
+                         "Gemma decoder for mubasun, a dense Mubasun for ninisun, the MoE Mubasun and Ninisun for birizen, Ninisun and Birizen for "
+                         "gogivik), "
                          "one GPU")
     ap.add_argument("--arch-sizes", default="w1024,w2048")
     args = ap.parse_args()

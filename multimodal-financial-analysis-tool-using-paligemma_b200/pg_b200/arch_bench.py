@@ -4,6 +4,10 @@ width, depth, query width and feed-forward size, with a per-kernel roofline tabl
 `bench.py --arch ninisun`: the same for the Ninisun engine beside the closest model the framework serves the same
 way, a dense Mubasun of equal width, depth, head layout, window and feed-forward width (`run_ninisun`).
 
+`bench.py --arch gogivik`: the Gogivik engine beside the two models that hold its closest kernels: Ninisun (attention in
+a mask, dense feed-forward, a recurrence with a gated norm) and Birizen (latent attention with a sink, the decayed
+linear-attention scan the state-space layer runs on) (`run_gogivik`).
+
 Timing: CUDA events on the launching stream, >= 3 warm-up steps, an L2-sized scratch write between timed steps.
 Roofline of an op = max(algorithmic FLOPs / measured bf16 peak, algorithmic bytes / measured copy bandwidth);
 `frac` = that time / measured time (1.0 = on the roofline)."""
@@ -718,6 +722,207 @@ def run_birizen(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048
         torch.cuda.empty_cache()
         cmpr = {}
         for like, other in ((BIRIZEN_LIKE_MUBASUN, mrow), (BIRIZEN_LIKE_NINISUN, nrow)):
+            for a, bname in like:
+                if a in row["prefill_ops"] and bname in other["prefill_ops"]:
+                    fa, fb = row["prefill_ops"][a]["frac"], other["prefill_ops"][bname]["frac"]
+                    cmpr[a] = {"frac": fa, "like": bname, "like_frac": fb, "distance_ratio": round(fb / fa, 2) if fa > 0 else None}
+        row["like_for_like"] = cmpr
+        result[name] = row
+    result["gpu_launches"] = int(cabi.launch_count() - launches0)
+    return result
+
+
+# ---------------------------------------------------------------------------------------------------------------
+GOGIVIK_SIZES = {
+    # latent layers as Birizen's (window added), attention layers as Ninisun's head layout (blocks instead of a window,
+    # per-head norms, rotated values), a state-space layer of inner width 2 x width: ssm_heads x ssm_vdim, state, groups
+    "w1024": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, vdim=128, rot_dim=64, q_rank=384, kv_rank=192, window=512,
+                  chunk=512, ssm_heads=32, ssm_vdim=64, state=128, groups=1, norm_groups=1, conv=4, taps=4, ff=4096, vocab=32000),
+    "w2048": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, vdim=128, rot_dim=64, q_rank=768, kv_rank=192, window=1024,
+                  chunk=1024, ssm_heads=64, ssm_vdim=64, state=128, groups=1, norm_groups=1, conv=4, taps=4, ff=8192, vocab=32000),
+}
+
+
+def gogivik_config(s: dict) -> dict:
+    """latent, attention, mamba2, attention, ... (every branch of the design is on the path)."""
+    layers = []
+    for i in range(s["layers"]):
+        if i % 4 == 0:
+            L = {"type": "latent_attention", "mixer": {
+                "heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["vdim"], "q_rank": s["q_rank"],
+                "kv_rank": s["kv_rank"], "scale": 1.0 / math.sqrt(s["dim"] + s["rot_dim"]), "mask": {"size": s["window"]},
+                "rot": {"dims": s["rot_dim"], "base": 10000.0}}}
+        elif i % 4 == 2:
+            L = {"type": "mamba2", "mixer": {"heads": s["ssm_heads"], "vdim": s["ssm_vdim"], "state": s["state"],
+                                             "groups": s["groups"], "norm_groups": s["norm_groups"], "conv": s["conv"]}}
+        else:
+            L = {"type": "attention", "mixer": {
+                "heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"],
+                "scale": 1.0 / math.sqrt(s["dim"]), "mask": {"size": s["chunk"]},
+                "rot": {"dims": s["dim"], "base": 10000.0, "scaling": {"factor": 2.0}}}}
+        L["mlp"] = {"kind": "dense", "ff": s["ff"]}
+        layers.append(L)
+    return {"architecture": "Gogivik", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "canon": {"taps": s["taps"]}, "logit_scale": 1.0, "layers": layers}
+
+
+def random_gogivik_weights(cfg: dict, device, dtype, seed=0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(seed)
+    D, out, taps = cfg["width"], {}, cfg["canon"]["taps"]
+
+    def lin(name, o, i, gain=1.0):
+        out[name] = (torch.randn(o, i, generator=g, device=device) * (gain / math.sqrt(i))).to(dtype)
+
+    def vec(name, n, mean=0.0, std=0.1):
+        out[name] = (mean + std * torch.randn(n, generator=g, device=device)).to(dtype)
+
+    out["embed"] = torch.randn(cfg["vocab"], D, generator=g, device=device).to(dtype)
+    lin("head", cfg["vocab"], D)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        for n in ("norm1", "norm2"):
+            vec(p + n, D)
+        for n in ("canon1", "canon2"):
+            out[p + n] = (0.2 * torch.randn(D, taps, generator=g, device=device)).to(dtype)
+        if L["type"] == "latent_attention":
+            H = m["heads"]
+            lin(p + "mix.dq", m["q_rank"], D), vec(p + "mix.dq.norm", m["q_rank"], 1.0)
+            lin(p + "mix.uq", H * (m["dim"] + m["rot_dim"]), m["q_rank"])
+            lin(p + "mix.dkv", m["kv_rank"] + m["rot_dim"], D), vec(p + "mix.dkv.norm", m["kv_rank"], 1.0)
+            lin(p + "mix.uk", H * m["dim"], m["kv_rank"]), lin(p + "mix.uv", H * m["vdim"], m["kv_rank"])
+            vec(p + "mix.sink", H, 0.0, 1.0), lin(p + "mix.o", D, H * m["vdim"])
+        elif L["type"] == "attention":
+            H, G = m["heads"], m["kv_heads"]
+            lin(p + "mix.q", H * m["dim"], D), lin(p + "mix.k", G * m["dim"], D), lin(p + "mix.v", G * m["vdim"], D)
+            vec(p + "mix.q.norm", m["dim"], 1.0), vec(p + "mix.k.norm", m["dim"], 1.0), lin(p + "mix.o", D, H * m["vdim"])
+        else:
+            inner, ch = m["heads"] * m["vdim"], m["heads"] * m["vdim"] + 2 * m["groups"] * m["state"]
+            lin(p + "mix.in", inner + ch + m["heads"], D)
+            out[p + "mix.conv"] = (0.3 * torch.randn(ch, m["conv"], generator=g, device=device)).to(dtype)
+            vec(p + "mix.conv.b", ch), vec(p + "mix.dt_bias", m["heads"], -1.0, 0.5), vec(p + "mix.A_log", m["heads"], -1.0, 0.5)
+            vec(p + "mix.D", m["heads"], 1.0), vec(p + "mix.norm", inner, 1.0), lin(p + "mix.o", D, inner)
+        lin(p + "mlp.up", L["mlp"]["ff"], D), lin(p + "mlp.down", D, L["mlp"]["ff"])
+    vec("final.norm", D)
+    return out
+
+
+def gogivik_work(s: dict, cfg: dict, T1: int, seqs: int) -> Dict[str, tuple]:
+    """name -> (FLOPs, bytes) of one step over `seqs` prompts of T1 tokens (bf16 operands, fp32 residual stream, fp32
+    normed rows into the input convolutions, fp32 scan records and state)."""
+    T, D, F = T1 * seqs, s["width"], s["ff"]
+    w: Dict[str, List[float]] = {}
+
+    def add(name, flops, nbytes):
+        a = w.setdefault(name, [0.0, 0.0])
+        a[0] += flops
+        a[1] += nbytes
+
+    def gemm(name, N, K):
+        add(name, 2 * T * N * K, 2 * (T * K + N * K + T * N))
+
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        add("norm", 0, 2 * T * D * (4 + 2 + 4 + 4))                       # x, y in; x, the normed row (fp32) out: both sublayers
+        add("input_conv", 0, 2 * T * D * (4 + 2))
+        if L["type"] == "latent_attention":
+            H, dim, vdim, rot, qr, kr, W = m["heads"], m["dim"], m["vdim"], m["rot_dim"], m["q_rank"], m["kv_rank"], m["mask"]["size"]
+            hq, hv, ldq = H * (dim + rot), H * vdim, kr + rot
+            keys = seqs * sum(min(i + 1, W) for i in range(T1))
+            gemm("proj", qr + kr + rot, D)
+            add("latent_prep", 0, 2 * T * (2 * qr + 2 * (kr + rot)))
+            gemm("q_up", hq, qr)
+            add("q_absorb", 2 * T * H * dim * kr, 2 * (T * hq + H * dim * kr + T * H * ldq))
+            add("latent_attention", 2 * keys * H * (ldq + kr), 2 * T * H * (ldq + kr) + 2 * T * ldq)
+            add("v_up", 2 * T * H * kr * vdim, 2 * (T * H * kr + H * vdim * kr + T * hv))
+            gemm("o", D, hv)
+        elif L["type"] == "attention":
+            H, G, dim, vdim, C = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]
+            keys = seqs * sum(i % C + 1 for i in range(T1))
+            n = H * dim + G * dim + G * vdim
+            gemm("proj", n, D)
+            add("headnorm_rotary_append", 0, 2 * 2 * T * n)
+            add("attention", 2 * keys * H * (dim + vdim), 2 * T * (H * dim + H * vdim + G * dim + G * vdim))
+            gemm("o", D, H * vdim)
+        else:
+            H, e, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            inner, ch = H * e, H * e + 2 * G * N
+            rec = H * (2 * N + e + 4)
+            gemm("proj", inner + ch + H, D)
+            add("ssm_prep", 0, T * (2 * (ch + H) + 4 * rec))
+            add("ssm_scan", 4 * T * H * N * e, T * 4 * (rec + inner))        # fp32 FMAs, not tensor work
+            add("gate_groupnorm", 0, T * inner * (4 + 2 + 2))
+            gemm("o", D, inner)
+        gemm("up", F, D)
+        add("relu2", 0, T * F * (2 + 2))
+        gemm("down", D, F)
+    add("head", 2 * seqs * D * s["vocab"], 2 * D * s["vocab"])
+    return {k: (v[0], v[1]) for k, v in w.items()}
+
+
+def _gogivik_decode_bytes(s: dict, cfg: dict) -> float:
+    """Weight bytes one decode step must stream."""
+    D, n = s["width"], 0.0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "latent_attention":
+            H = m["heads"]
+            n += D * (m["q_rank"] + m["kv_rank"] + m["rot_dim"] + H * m["vdim"]) + m["q_rank"] * H * (m["dim"] + m["rot_dim"]) + \
+                H * m["kv_rank"] * (m["dim"] + m["vdim"])
+        elif L["type"] == "attention":
+            n += D * (2 * m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"]))
+        else:
+            inner = m["heads"] * m["vdim"]
+            n += D * (3 * inner + 2 * m["groups"] * m["state"] + m["heads"])
+        n += 2 * D * L["mlp"]["ff"]
+    return 2.0 * (n + D * s["vocab"])
+
+
+GOGIVIK_LIKE_NINISUN = [("proj", "proj"), ("o", "o"), ("up", "gate_up"), ("down", "down"), ("attention", "attention"),
+                        ("headnorm_rotary_append", "rotary_append"), ("gate_groupnorm", "headnorm_gate"), ("norm", "post_norm"),
+                        ("input_conv", "post_norm"), ("relu2", "headnorm_gate"), ("head", "head")]
+GOGIVIK_LIKE_BIRIZEN = [("latent_prep", "latent_prep"), ("q_up", "q_up"), ("q_absorb", "q_absorb"),
+                        ("latent_attention", "latent_attention"), ("v_up", "v_up_gate"), ("ssm_scan", "lightning"),
+                        ("ssm_prep", "lightning_prep")]
+
+
+@torch.no_grad()
+def run_gogivik(sizes, steps: int, warmup: int, peaks: dict, prefill_tokens=2048, prefill_seqs=4, context=1024,
+                decode_batches=(1, 8)) -> dict:
+    from .birizen import BirizenEngine
+    from .gogivik import GogivikEngine
+    from .ninisun import NinisunEngine
+    dev, dtype = torch.device("cuda:0"), torch.bfloat16
+    timer = _Timer()
+    result = {}
+    launches0 = cabi.launch_count()
+    pool = (max(max(decode_batches), prefill_seqs) + 1) * (max(prefill_tokens, context) + 256)
+    for name in sizes:
+        s = GOGIVIK_SIZES[name]
+        cfg = gogivik_config(s)
+        eng = GogivikEngine(cfg, random_gogivik_weights(cfg, dev, dtype), device=dev, dtype=dtype, kv_pool_tokens=pool)
+        row = {"size": s}
+        row.update(_measure_ragged(eng, s["vocab"], timer, steps, warmup, peaks, gogivik_work(s, cfg, prefill_tokens, prefill_seqs),
+                                   lambda B: _gogivik_decode_bytes(s, cfg), prefill_tokens, prefill_seqs, context, decode_batches))
+        del eng
+        torch.cuda.empty_cache()
+        ns_ = NINISUN_SIZES[name]
+        ncfg = ninisun_config(ns_)
+        neng = NinisunEngine(ncfg, random_ninisun_weights(ncfg, ns_, dev, dtype), device=dev, dtype=dtype, kv_pool_tokens=pool)
+        nrow = _measure_ragged(neng, ns_["vocab"], timer, steps, warmup, peaks, ninisun_work(ns_, ncfg, prefill_tokens, prefill_seqs),
+                               lambda B: _ninisun_decode_bytes(ns_, ncfg), prefill_tokens, prefill_seqs, context, decode_batches)
+        row["ninisun_equal_size"] = nrow
+        del neng
+        torch.cuda.empty_cache()
+        bs_ = BIRIZEN_SIZES[name]
+        bcfg = birizen_config(bs_)
+        beng = BirizenEngine(bcfg, random_birizen_weights(bcfg, dev, dtype), device=dev, dtype=dtype, kv_pool_tokens=pool)
+        brow = _measure_ragged(beng, bs_["vocab"], timer, steps, warmup, peaks, birizen_work(bs_, bcfg, prefill_tokens, prefill_seqs),
+                               lambda B: _birizen_decode_bytes(bs_, bcfg, B), prefill_tokens, prefill_seqs, context, decode_batches)
+        row["birizen_equal_size"] = brow
+        del beng
+        torch.cuda.empty_cache()
+        cmpr = {}
+        for like, other in ((GOGIVIK_LIKE_NINISUN, nrow), (GOGIVIK_LIKE_BIRIZEN, brow)):
             for a, bname in like:
                 if a in row["prefill_ops"] and bname in other["prefill_ops"]:
                     fa, fb = row["prefill_ops"][a]["frac"], other["prefill_ops"][bname]["frac"]
