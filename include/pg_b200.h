@@ -520,6 +520,13 @@ int pg_group_rmsnorm_ex(void* out, float* x, const void* add_a, int lda, const v
                         int dtype, void* stream);
 int pg_time_conv_residual(void* out, const float* in, const void* w, const float* state, const int32_t* tok_slot,
                           int n_tokens, int C, int taps, int dtype, void* stream);
+/* pg_norm_time_conv: pg_group_rmsnorm_ex (one group, fp32) + pg_time_conv_residual + pg_time_conv_state in one pass and a
+ * small second launch: x_out = x_in + y (y may be NULL; x_out must not alias x_in), out = n + conv(n) with
+ * n = RMS(x_out) * (w_norm or 1 + w_norm), then the sequences' states [slots][taps - 1][D] of normed rows are brought up
+ * to the end of the step's segments.  taps <= 8. */
+int pg_norm_time_conv(void* out, float* x_out, const float* x_in, const void* y, int ldy, const void* w_norm, int one_plus,
+                      float eps, const void* w_conv, float* state, const int32_t* tok_slot, const int32_t* segs, int n_segs,
+                      int n_tokens, int D, int taps, int dtype, void* stream);
 int pg_time_conv_state(float* state, const void* src, int ld, int col0, int src_f32, const int32_t* segs, int n_segs,
                        int C, int taps, int dtype, void* stream);
 int pg_headnorm_rotary_append(void* q_out, const void* proj, int ld, int q_col0, int n_heads, int k_col0, int n_kv_heads,

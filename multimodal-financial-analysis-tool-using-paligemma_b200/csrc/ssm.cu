@@ -8,7 +8,8 @@
 // This is the recurrence of the decayed linear-attention kernel (recurrent.cu) with key step * B, value x, query C, a
 // decay per (token, head) and a skip term; ssm_prep_kernel writes exactly its records and that kernel runs the scan.
 //
-// ssm_prep_kernel       (CTA per token): the convolution reads the token's own row and the taps - 1 inputs before it,
+// ssm_prep_kernel       (CTA per token; every channel is convolved once into shared memory, then the records of all
+//                       heads are written from there): the convolution reads the token's own row and the taps - 1 inputs before it,
 //                       rows of the same step where the sequence has them, else the slot's convolution state
 //                       (timeconv.cu keeps it: the last taps - 1 projected inputs, fp32); conv, silu, softplus and
 //                       both exponentials in fp32.  One packed fp32 record per (token, head):
@@ -29,9 +30,10 @@ ssm_prep_kernel(float* __restrict__ rec, const T* __restrict__ proj, int ld, int
                 const T* __restrict__ conv_w, const T* __restrict__ conv_b, const float* __restrict__ conv_state,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const int32_t* __restrict__ tok_slot,
                 int heads, int vdim, int N, int groups, int taps, int np, int vp) {
-  extern __shared__ float sm[];                    // [heads] step | [heads] decay
+  extern __shared__ float sm[];                    // [heads] step | [heads] decay | [channels] silu(conv) of x, B, C
   float* step = sm;
   float* decay = sm + heads;
+  float* act = sm + 2 * heads;
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, K = taps - 1, inner = heads * vdim, channels = inner + 2 * groups * N;
@@ -44,28 +46,28 @@ ssm_prep_kernel(float* __restrict__ rec, const T* __restrict__ proj, int ld, int
     step[h] = s;
     decay[h] = expf(-expf(a_log[h]) * s);
   }
+  // every channel once (B and C are shared by the heads of a group): consecutive threads, consecutive channels
+  for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) {
+    const T* wc = conv_w + (size_t)ch * taps;
+    float acc = to_f<T>(conv_b[ch]);
+    acc = fmaf(to_f<T>(row[xbc_col0 + ch]), to_f<T>(wc[K]), acc);
+    for (int j = 1; j <= K; ++j) {
+      const float u = j <= before ? to_f<T>(proj[(size_t)(t - j) * ld + xbc_col0 + ch])
+                                  : conv_state[((size_t)slot * K + (K - (j - before))) * channels + ch];
+      acc = fmaf(u, to_f<T>(wc[K - j]), acc);
+    }
+    act[ch] = ssm_silu(acc);
+  }
   __syncthreads();
   const int rs = 2 * np + vp + 4, hpg = heads / groups;
   float* out = rec + (size_t)t * heads * rs;
   for (int i = threadIdx.x; i < heads * rs; i += blockDim.x) {
     const int h = i / rs, c = i - h * rs, g = h / hpg;
-    int ch = -1;                                   // channel of [x | B | C]
-    float mul = 1.f;
-    if (c < np) { if (c < N) ch = inner + groups * N + g * N + c; }
-    else if (c < 2 * np) { if (c - np < N) { ch = inner + g * N + (c - np); mul = step[h]; } }
-    else if (c < 2 * np + vp) { if (c - 2 * np < vdim) ch = h * vdim + (c - 2 * np); }
-    float v = c == 2 * np + vp ? decay[h] : 0.f;
-    if (ch >= 0) {
-      const T* wc = conv_w + (size_t)ch * taps;
-      float acc = to_f<T>(conv_b[ch]);
-      acc = fmaf(to_f<T>(row[xbc_col0 + ch]), to_f<T>(wc[K]), acc);
-      for (int j = 1; j <= K; ++j) {
-        const float u = j <= before ? to_f<T>(proj[(size_t)(t - j) * ld + xbc_col0 + ch])
-                                    : conv_state[((size_t)slot * K + (K - (j - before))) * channels + ch];
-        acc = fmaf(u, to_f<T>(wc[K - j]), acc);
-      }
-      v = ssm_silu(acc) * mul;
-    }
+    float v = 0.f;
+    if (c < np) { if (c < N) v = act[inner + groups * N + g * N + c]; }
+    else if (c < 2 * np) { if (c - np < N) v = act[inner + g * N + (c - np)] * step[h]; }
+    else if (c < 2 * np + vp) { if (c - 2 * np < vdim) v = act[h * vdim + (c - 2 * np)]; }
+    else if (c == 2 * np + vp) v = decay[h];
     out[i] = v;
   }
 }
@@ -107,7 +109,8 @@ extern "C" int pg_ssm_prep(float* rec, const void* proj, int ld, int xbc_col0, i
              groups, taps);
   const int np = (state + 3) / 4 * 4, vp = (vdim + 3) / 4 * 4;
   PG_DISPATCH_DTYPE(dtype, T, {
-    return launch_pdl("ssm_prep", ssm_prep_kernel<T>, dim3(n_tokens), dim3(256), sizeof(float) * 2 * heads,
+    const size_t smem = sizeof(float) * (2 * (size_t)heads + (size_t)heads * vdim + 2 * (size_t)groups * state);
+    return launch_pdl("ssm_prep", ssm_prep_kernel<T>, dim3(n_tokens), dim3(256), smem,
                       (cudaStream_t)stream, rec, (const T*)proj, ld, xbc_col0, dt_col0, (const T*)conv_w, (const T*)conv_b,
                       conv_state, dt_bias, a_log, tok_slot, heads, vdim, state, groups, taps, np, vp);
   });

@@ -111,6 +111,7 @@ SIGNATURES = {
     # norms stored around zero, convolutions over time, per-head norms + rotated values, blocked masks, state-space mixer
     "pg_group_rmsnorm_ex": [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _vp],
     "pg_time_conv_residual": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pg_norm_time_conv": [_vp, _vp, _vp, _vp, _i, _vp, _i, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "pg_time_conv_state": [_vp, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _vp],
     "pg_headnorm_rotary_append": [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _i, _i, _vp, _i, _vp, _vp,
                                   _vp, _i, _i, _vp, _vp, _i, _i, _vp],

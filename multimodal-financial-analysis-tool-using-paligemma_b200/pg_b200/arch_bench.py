@@ -822,8 +822,9 @@ def gogivik_work(s: dict, cfg: dict, T1: int, seqs: int) -> Dict[str, tuple]:
 
     for L in cfg["layers"]:
         m = L["mixer"]
-        add("norm", 0, 2 * T * D * (4 + 2 + 4 + 4))                       # x, y in; x, the normed row (fp32) out: both sublayers
-        add("input_conv", 0, 2 * T * D * (4 + 2))
+        add("norm_conv", 0, 2 * T * D * (4 + 2 + 4 + 2))                  # x, y in; x, h out: both sublayers (fused kernel)
+        add("norm", 0, 2 * T * D * (4 + 2 + 4 + 4))                       # the separate kernels (PG_GOGIVIK_FUSED_READ=0):
+        add("input_conv", 0, 2 * T * D * (4 + 2))                         # x, y in; x, normed fp32 row out | normed row in, h out
         if L["type"] == "latent_attention":
             H, dim, vdim, rot, qr, kr, W = m["heads"], m["dim"], m["vdim"], m["rot_dim"], m["q_rank"], m["kv_rank"], m["mask"]["size"]
             hq, hv, ldq = H * (dim + rot), H * vdim, kr + rot
@@ -879,7 +880,7 @@ def _gogivik_decode_bytes(s: dict, cfg: dict) -> float:
 
 GOGIVIK_LIKE_NINISUN = [("proj", "proj"), ("o", "o"), ("up", "gate_up"), ("down", "down"), ("attention", "attention"),
                         ("headnorm_rotary_append", "rotary_append"), ("gate_groupnorm", "headnorm_gate"), ("norm", "post_norm"),
-                        ("input_conv", "post_norm"), ("relu2", "headnorm_gate"), ("head", "head")]
+                        ("input_conv", "post_norm"), ("norm_conv", "post_norm"), ("relu2", "headnorm_gate"), ("head", "head")]
 GOGIVIK_LIKE_BIRIZEN = [("latent_prep", "latent_prep"), ("q_up", "q_up"), ("q_absorb", "q_absorb"),
                         ("latent_attention", "latent_attention"), ("v_up", "v_up_gate"), ("ssm_scan", "lightning"),
                         ("ssm_prep", "lightning_prep")]

@@ -36,6 +36,7 @@ the decayed linear-attention kernel with a decay per token.
 """
 from __future__ import annotations
 
+import os
 import warnings
 from dataclasses import dataclass, field
 from typing import Dict, List, Mapping, Optional
@@ -144,6 +145,8 @@ class GogivikEngine(LatentAttentionMixin, RaggedEngine):
         self.cfg = config if isinstance(config, GogivikConfig) else GogivikConfig.from_dict(config)
         self.strict = bool(strict)      # True: tensors the config does not call for raise instead of being reported
         self._init_common(device=device, dtype=dtype, page_size=page_size, gemm_impl=gemm_impl)
+        # residual sum + norm + input convolution as one kernel (0: the three separate kernels, for comparison)
+        self.fused_read = os.environ.get("PG_GOGIVIK_FUSED_READ", "1") != "0"
         self._repack(weights)
         L_ = cabi.lib()
         for w, lc in zip(self.layers, self.cfg.layers):
@@ -233,24 +236,32 @@ class GogivikEngine(LatentAttentionMixin, RaggedEngine):
         return SlotState(slots, shapes, self.device)
 
     # ------------------------------------------------------------------ one step
-    def _read(self, kv, inp: StepInputs, key, x, y, w_norm, w_conv) -> torch.Tensor:
+    def _read(self, kv, inp: StepInputs, key, x, x_alt, y, w_norm, w_conv):
         """What a sublayer reads: x += y (the sublayer output not yet summed in; None: nothing), n = N(x) in fp32,
-        h = n + conv(n) over the sequence's positions, the state of the sequence brought up to this step's end."""
+        h = n + conv(n) over the sequence's positions, the state of the sequence brought up to this step's end.  Returns
+        (h, the stream, the spare stream buffer): the fused kernel writes the sum into the spare buffer (a tile re-reads
+        rows that its neighbour owns), so the two change places."""
         L, st, tm, c = cabi.lib(), cabi.stream(), self._tm, self.cfg
         T, D = x.shape
+        h = self._new(T, D)
+        state = kv.state.layers[key] if c.taps > 1 else None
+        if self.fused_read and c.taps <= 8:
+            with tm("norm_conv"):
+                cabi.check(L.pg_norm_time_conv(ptr(h), ptr(x_alt), ptr(x), ptr(y), 0 if y is None else y.stride(0), ptr(w_norm), 1,
+                                               c.eps, ptr(w_conv), ptr(state), ptr(inp.slot), ptr(inp.segs), inp.n_segs, T, D,
+                                               c.taps, self.dt, st), "norm_time_conv")
+            return h, x_alt, x
         n = self._new(T, D, dtype=torch.float32)
         with tm("norm"):
             cabi.check(L.pg_group_rmsnorm_ex(ptr(n), ptr(x), ptr(y), 0 if y is None else y.stride(0), None, 0, ptr(w_norm),
                                              None, T, D, 1, c.eps, 1, 1, self.dt, st), "rmsnorm")
-        h = self._new(T, D)
-        state = kv.state.layers[key] if c.taps > 1 else None
         with tm("input_conv"):
             cabi.check(L.pg_time_conv_residual(ptr(h), ptr(n), ptr(w_conv), ptr(state), ptr(inp.slot), T, D, c.taps,
                                                self.dt, st), "time_conv_residual")
             if state is not None:
                 cabi.check(L.pg_time_conv_state(ptr(state), ptr(n), D, 0, 1, ptr(inp.segs), inp.n_segs, D, c.taps, self.dt,
                                                 st), "time_conv_state")
-        return h
+        return h, x, x_alt
 
     def _attention(self, kv, inp: StepInputs, li: int, a: BlockAttnCfg, w: dict, h) -> torch.Tensor:
         L, st, tm, T, at = cabi.lib(), cabi.stream(), self._tm, inp.T, w["at"]
@@ -310,12 +321,12 @@ class GogivikEngine(LatentAttentionMixin, RaggedEngine):
         T, nw, D = inp.T, inp.nw, self.cfg.width
         if kv.state is None:
             raise RuntimeError("this step's slot table carries no per-sequence state for the model's convolutions")
-        x = self._new(T, D, dtype=torch.float32)
+        x, x_alt = self._new(T, D, dtype=torch.float32), self._new(T, D, dtype=torch.float32)
         cabi.check(L.pg_embed_pos(ptr(x), ptr(inp.ids), None, ptr(self.emb), None, T, D, c.vocab, 0, 1.0, ptr(self.err_flag),
                                   self.dt, st), "embed")
         y = None                                            # a sublayer's output that the next norm kernel sums into x
         for li, (lc, w) in enumerate(zip(c.layers, self.layers)):
-            h = self._read(kv, inp, ("canon1", li), x, y, w["norm1"], w["canon1"])
+            h, x, x_alt = self._read(kv, inp, ("canon1", li), x, x_alt, y, w["norm1"], w["canon1"])
             if lc.kind == "latent_attention":
                 y = self._latent(kv, inp, self.c_pools[li], lc.mixer, w, h)
             elif lc.kind == "attention":
@@ -323,7 +334,7 @@ class GogivikEngine(LatentAttentionMixin, RaggedEngine):
             else:
                 y = self._ssm(kv, inp, li, lc.mixer, w, h)
             if lc.ff:
-                h = self._read(kv, inp, ("canon2", li), x, y, w["norm2"], w["canon2"])
+                h, x, x_alt = self._read(kv, inp, ("canon2", li), x, x_alt, y, w["norm2"], w["canon2"])
                 with tm("up"):
                     u = self._linear(h, w["up"])
                 with tm("relu2"):

@@ -105,6 +105,54 @@ def test_input_convolution_over_portions_slots_and_state(taps, C, dtype):
         _close(torch.cat(got[k]), want[k], 4e-3 if dtype == torch.bfloat16 else 2e-6)
 
 
+@pytest.mark.parametrize("taps,D", [(4, 40), (2, 7), (8, 300), (1, 16), (3, 1030)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sum_norm_and_input_convolution_in_one_kernel(taps, D, dtype):
+    """The fused kernel (tiles of 16 rows that start anywhere in a sequence) against the oracle over whole sequences:
+    portions of 1, 2, 17 and 40 tokens side by side, sequences that start inside a tile, a slot handed on."""
+    cabi, L, st = _lib()
+    g = torch.Generator().manual_seed(taps * 1000 + D)
+    lens = {"a": 71, "b": 30, "c": 21}
+    xs = {k: torch.randn(n, D, generator=g) * 2 for k, n in lens.items()}
+    ys = {k: torch.randn(n, D + 8, generator=g).to(dtype) for k, n in lens.items()}
+    wn = (0.3 * torch.randn(D, generator=g)).to(dtype)
+    wc = (0.5 * torch.randn(D, taps, generator=g)).to(dtype)
+    sums = {k: xs[k].to(F64) + ys[k][:, :D].to(F64) for k in lens}
+    want = {k: O.input_conv(O.norm_one_plus(sums[k], wn.float(), 1e-4), wc.float()) for k in lens}
+    slot = {"a": 2, "b": 0, "c": 2}
+    state = torch.randn(3, max(taps - 1, 1), D, generator=g).cuda()
+    wnd, wcd = wn.cuda(), wc.cuda()
+    plan = [[("a", 1), ("b", 2)], [("b", 1), ("a", 2)], [("a", 17), ("b", 5)], [("a", 40), ("b", 21)], [("b", 1), ("a", 11)],
+            [("c", 2)], [("c", 1)], [("c", 18)]]
+    fed = {k: 0 for k in lens}
+    got = {k: [] for k in lens}
+    for step in plan:
+        for k, _ in step:
+            if fed[k] == 0:
+                state[slot[k]].zero_()
+        x_in = torch.cat([xs[k][fed[k]:fed[k] + n] for k, n in step]).cuda()
+        y = torch.cat([ys[k][fed[k]:fed[k] + n] for k, n in step]).cuda()
+        T = x_in.shape[0]
+        out, x_out = torch.zeros(T, D, dtype=dtype, device="cuda"), torch.zeros(T, D, device="cuda")
+        slots = [slot[k] for k, n in step for _ in range(n)]
+        segs = _segs([n for _, n in step], [slot[k] for k, _ in step]) + [1, 0, 0]
+        before = state.clone()
+        cabi.check(L.pg_norm_time_conv(out.data_ptr(), x_out.data_ptr(), x_in.data_ptr(), y.data_ptr(), D + 8, wnd.data_ptr(), 1, 1e-4,
+                                       wcd.data_ptr(), state.data_ptr(), _i32(slots).data_ptr(), _i32(segs).data_ptr(),
+                                       len(segs) // 3, T, D, taps, CT[dtype], st))
+        at = 0
+        for k, n in step:
+            got[k].append(out[at:at + n].float().cpu())
+            _close(x_out[at:at + n], sums[k][fed[k]:fed[k] + n], 1e-6)
+            at += n
+            fed[k] += n
+        for s in (s for s in range(3) if s not in slots):
+            assert torch.equal(state[s], before[s])
+    for k in lens:
+        assert fed[k] == lens[k]
+        _close(torch.cat(got[k]), want[k], 4e-3 if dtype == torch.bfloat16 else 2e-6)
+
+
 @pytest.mark.parametrize("H,G,dim,vdim,rot_dims,factor", [(4, 2, 12, 10, 8, 4.0), (3, 3, 16, 16, 16, None), (8, 1, 64, 32, 32, 2.0),
                                                           (2, 1, 6, 2, 0, None), (16, 4, 128, 128, 128, 1.5)])
 def test_head_norms_rotation_of_keys_and_values_and_cache_append(H, G, dim, vdim, rot_dims, factor):
@@ -451,6 +499,21 @@ def _oracle(name, n, seed=0):
         sink = []
         _ORACLE_CACHE[key] = (toks, O.forward(cfg, ck, toks, sink), sink)
     return _ORACLE_CACHE[key]
+
+
+def test_separate_kernels_for_the_sublayer_input_give_the_same(monkeypatch):
+    """The three separate kernels (sum + norm, convolution, state) stay as the path for more than 8 taps."""
+    name, n = "small", 90
+    toks, want, _ = _oracle(name, n)
+    monkeypatch.setenv("PG_GOGIVIK_FUSED_READ", "0")
+    eng, _ = _engine(CONFIGS[name])
+    assert not eng.fused_read
+    b = eng.new_batcher(slots=1)
+    b.admit("a")
+    got = [b.run_entries([("a", toks[:33], list(range(33)))]), b.run_entries([("a", toks[33:35], [0, 1])])]
+    got += [b.run_entries([("a", [t], [0])]) for t in toks[35:]]
+    _rows_close(torch.cat(got), want, 6e-5)
+    b.close()
 
 
 def test_taps_of_two():
