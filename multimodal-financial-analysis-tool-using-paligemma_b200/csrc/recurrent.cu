@@ -509,7 +509,14 @@ extern "C" int pg_lightning_attention_ex(float* out, float* state, const float* 
   // lanes per value column: a thread keeps DMAX / RG state elements, and a token is that many fused multiply-adds
   // twice plus log2(RG) shuffle steps on the critical path of the recurrence
   if (dim <= 32) return launch_lightning<32, 4, 16>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
-  if (dim <= 64) return launch_lightning<64, 8, 8>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
-  if (dim <= 128) return launch_lightning<128, 8, 8>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
+  // tokens per buffer: the next buffer's records must be on their way for longer than a DRAM round trip while this
+  // one is consumed (16 tokens of 64..128 key channels; 8 left the recurrence waiting on every refill)
+  static const int deep = env_int("PG_LIGHTNING_DEEP", 1);
+  if (dim <= 64)
+    return deep ? launch_lightning<64, 8, 16>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st)
+                : launch_lightning<64, 8, 8>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
+  if (dim <= 128)
+    return deep ? launch_lightning<128, 8, 16>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st)
+                : launch_lightning<128, 8, 8>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
   return launch_lightning<256, 16, 4>(out, state, rec, decay, skip, td, segs, n_segs, heads, dim, vdim, st);
 }
