@@ -59,16 +59,30 @@ ssm_prep_kernel(float* __restrict__ rec, const T* __restrict__ proj, int ld, int
     act[ch] = ssm_silu(acc);
   }
   __syncthreads();
-  const int rs = 2 * np + vp + 4, hpg = heads / groups;
-  float* out = rec + (size_t)t * heads * rs;
-  for (int i = threadIdx.x; i < heads * rs; i += blockDim.x) {
-    const int h = i / rs, c = i - h * rs, g = h / hpg;
-    float v = 0.f;
-    if (c < np) { if (c < N) v = act[inner + groups * N + g * N + c]; }
-    else if (c < 2 * np) { if (c - np < N) v = act[inner + g * N + (c - np)] * step[h]; }
-    else if (c < 2 * np + vp) { if (c - 2 * np < vdim) v = act[h * vdim + (c - 2 * np)]; }
-    else if (c == 2 * np + vp) v = decay[h];
-    out[i] = v;
+  // a warp per head writes its record in four floats per lane (np and vp are multiples of 4, so a vector never
+  // straddles two parts of the record)
+  const int rs = 2 * np + vp + 4, hpg = heads / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int h = warp; h < heads; h += blockDim.x >> 5) {
+    const int g = h / hpg;
+    const float* cq = act + inner + groups * N + g * N;      // C: the query
+    const float* bk = act + inner + g * N;                   // B: the key, times the step
+    const float* xv = act + h * vdim;                        // x: the value
+    const float sh = step[h];
+    float* out = rec + ((size_t)t * heads + h) * rs;
+    for (int c = lane * 4; c < rs; c += 128) {
+      float v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int cc = c + i;
+        float a = 0.f;
+        if (cc < np) { if (cc < N) a = cq[cc]; }
+        else if (cc < 2 * np) { if (cc - np < N) a = bk[cc - np] * sh; }
+        else if (cc < 2 * np + vp) { if (cc - 2 * np < vdim) a = xv[cc - 2 * np]; }
+        else if (cc == 2 * np + vp) a = decay[h];
+        v[i] = a;
+      }
+      *reinterpret_cast<float4*>(out + c) = make_float4(v[0], v[1], v[2], v[3]);
+    }
   }
 }
 
