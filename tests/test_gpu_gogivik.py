@@ -516,6 +516,63 @@ def test_separate_kernels_for_the_sublayer_input_give_the_same(monkeypatch):
     b.close()
 
 
+def _random_config(rng):
+    """Sizes, layer order and constants drawn at random from what real checkpoints use."""
+    div = lambda n: [d for d in range(1, n + 1) if n % d == 0]
+    layers = []
+    for _ in range(rng.randint(3, 6)):
+        kind = rng.choice(["latent", "attention", "mamba2"])
+        ff = rng.choice([0, 128, 256, 384])
+        if kind == "latent":
+            L = O.latent(heads=rng.choice([2, 3, 4, 6, 8]), dim=rng.choice([16, 24, 32, 64]), rot_dim=rng.choice([8, 16, 32, 64]),
+                         vdim=rng.choice([16, 32, 48, 64]), q_rank=rng.choice([32, 48, 80, 128]), kv_rank=rng.choice([32, 48, 64, 96, 192]),
+                         window=rng.choice([8, 31, 64, 72, 100, 1000]), base=rng.choice([1e4, 2.5e5]))
+        elif kind == "attention":
+            H, dim = rng.choice([2, 4, 6, 8, 12]), rng.choice([16, 32, 48, 64, 128])
+            L = O.attention(heads=H, kv_heads=rng.choice(div(H)), dim=dim, vdim=rng.choice([16, 32, 48, 64, 128]),
+                            chunk=rng.choice([8, 33, 64, 96, 150, 1000]), rot_dims=rng.choice([dim, dim // 2]),
+                            factor=rng.choice([None, 2.0, 4.0]), base=rng.choice([1e4, 2e4, 1e6]))
+        else:
+            H = rng.choice([2, 4, 6, 8])
+            L = O.mamba2(heads=H, vdim=rng.choice([16, 32, 64]), state=rng.choice([16, 32, 64, 128]), groups=rng.choice(div(H)),
+                         norm_groups=rng.choice(div(H)), conv=rng.choice([2, 3, 4]))
+        layers.append(O.layer(L, ff))
+    return O.make_config(width=rng.choice([128, 192, 256, 320]), vocab=rng.choice([300, 512]), layers=layers,
+                         taps=rng.choice([2, 3, 4, 5]), eps=rng.choice([1e-5, 1e-6]), logit_scale=rng.choice([1.0, 2.0, 0.7]))
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_models_drawn_at_random_whole_and_cut(seed):
+    """Layer order, head layouts, ranks, windows, blocks, taps and constants at random: a whole prompt and the same
+    tokens in portions and single tokens, in fp32 (every row) and in bf16 (typical error of a few percent)."""
+    import random
+    rng = random.Random(seed)
+    cfg = _random_config(rng)
+    ck = O.make_checkpoint(cfg, seed)
+    n = 160
+    toks = _tokens(n, cfg["vocab"], seed)
+    want = O.forward(cfg, ck, toks)
+    for dtype in (torch.float32, torch.bfloat16):
+        eng, _ = _engine(cfg, seed=seed, dtype=dtype)
+        b = eng.new_batcher(slots=2)
+        b.admit("w")
+        whole = b.run_entries([("w", toks, list(range(n)))])
+        b.finish("w")
+        b.admit("c")
+        at, got = 0, []
+        for size in [3, 61, 2, 50, 17]:
+            got.append(b.run_entries([("c", toks[at:at + size], list(range(size)))]))
+            at += size
+        got += [b.run_entries([("c", [t], [0])]) for t in toks[at:]]
+        eng.check_errors(sync=True)
+        b.close()
+        for out in (whole, torch.cat(got)):
+            if dtype == torch.float32:
+                _rows_close(out, want, 1e-4)
+            else:
+                _rows_close(out, want, 8e-2, 0.05)
+
+
 def test_taps_of_two():
     cfg = O.make_config(width=32, vocab=40, taps=2, layers=[O.layer(O.mamba2(heads=2, vdim=8, state=4, groups=1, norm_groups=2, conv=4), 16),
                                                             O.layer(O.attention(heads=2, kv_heads=1, dim=8, vdim=8, chunk=3), 16)])
