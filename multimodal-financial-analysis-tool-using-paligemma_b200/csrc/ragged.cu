@@ -538,7 +538,7 @@ extern "C" int pg_headnorm_rotary_append(void* q_out, const void* proj, int ld, 
              "headnorm_rotary_append: %d rotated columns of %d (even, with a frequency table)", rot_dims, dim);
   PG_REQUIRE(!v_freq || vdim % 2 == 0, "headnorm_rotary_append: rotated values need an even width, not %d", vdim);
   const int heads = n_heads + 2 * n_kv_heads;
-  const int threads = heads >= 16 ? 512 : (heads >= 8 ? 256 : 128);
+  const int threads = heads >= 32 ? 1024 : (heads < 4 ? 128 : 32 * heads);     // a warp per head while a CTA can hold them
   PG_DISPATCH_DTYPE(dtype, T, {
     return launch_pdl("headnorm_rotary_append", headnorm_rotary_append_kernel<T>, dim3(n_tokens), dim3(threads), 0,
                       (cudaStream_t)stream, (T*)q_out, (const T*)proj, ld, q_col0, n_heads, k_col0, n_kv_heads, dim, v_col0,

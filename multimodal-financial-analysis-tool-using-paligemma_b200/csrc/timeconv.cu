@@ -26,7 +26,8 @@
 //                             values in registers, refilled from the sequence's state where a sequence starts inside
 //                             the tile or the step.
 // norm_time_conv_state_kernel: the state update for that kernel, which leaves no normed rows behind: the K rows a segment
-//                             ends with are normed again from x_out (a CTA per segment).
+//                             ends with are normed again from x_out (a CTA per segment and entry; a segment shorter
+//                             than K also moves old entries down, in order, in one CTA).
 #include "common.cuh"
 
 namespace pg {
@@ -138,7 +139,7 @@ norm_time_conv_kernel(T* __restrict__ out, float* __restrict__ x_out, const floa
     const float* xr = x_in + (size_t)t * D;
     const T* yr = y ? y + (size_t)t * ldy : nullptr;
     float ss = 0.f;
-#pragma unroll 4
+#pragma unroll 8
     for (int c = lane * VEC; c < D; c += 32 * VEC) {
       float v[VEC];
       load_sum<T, VEC>(xr + c, yr ? yr + c : nullptr, v);
@@ -215,7 +216,11 @@ norm_time_conv_state_kernel(float* __restrict__ state, const float* __restrict__
   if (n <= 0) return;
   const float w0 = one_plus ? 1.f : 0.f;
   float* st = state + (size_t)slot * K * D;
-  for (int i = 0; i < K; ++i) {                    // entry i of the new state = entry n + i of [old state ; normed rows]
+  // a segment of K rows or more fills every entry from a row: one CTA per entry (blockIdx.y).  A shorter one also
+  // moves old entries down, in order: the first CTA does it all.
+  const bool split = n >= K;
+  if (!split && blockIdx.y != 0) return;
+  for (int i = split ? blockIdx.y : 0; i < (split ? blockIdx.y + 1 : K); ++i) {   // entry i of the new state = entry n + i of [old state ; normed rows]
     const int idx = n + i;
     if (idx < K) {
       for (int c = threadIdx.x; c < D; c += blockDim.x) st[(size_t)i * D + c] = st[(size_t)idx * D + c];
@@ -262,7 +267,7 @@ extern "C" int pg_norm_time_conv(void* out, float* x_out, const float* x_in, con
                         x_out, x_in, (const T*)y, ldy, (const T*)w_norm, one_plus, eps, (const T*)w_conv, (const float*)state,
                         tok_slot, n_tokens, D, taps);
     if (rc != PG_OK || taps == 1 || n_segs <= 0) return rc;
-    return launch_pdl("norm_time_conv_state", norm_time_conv_state_kernel<T>, dim3(n_segs), dim3(256), 0, st, state,
+    return launch_pdl("norm_time_conv_state", norm_time_conv_state_kernel<T>, dim3(n_segs, taps - 1), dim3(256), 0, st, state,
                       (const float*)x_out, (const T*)w_norm, one_plus, eps, segs, D, taps);
   });
   return PG_OK;
