@@ -23,7 +23,7 @@ FILES = ("modeling_gemma.py", "modeling_siglip.py", "processing_paligemma.py", "
 
 
 def build(src: str = "/root/reference") -> bool:
-    if not os.path.isdir(src):
+    if not all(os.path.isfile(os.path.join(src, f)) for f in FILES):      # no reference tree, or an empty one
         return False
     os.makedirs(OUT, exist_ok=True)
     lines = []
