@@ -76,3 +76,12 @@ def test_bench_stdout_carries_only_the_json_line():
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, check=True)
     assert r.stdout.strip().splitlines() == [json.dumps({"metric": "x", "value": 1.0})]
     assert "NCCL version" in r.stderr and "chatter" in r.stderr
+
+
+def test_staging_the_reference_from_an_absent_or_empty_tree_does_nothing(tmp_path):
+    """The build hook stages the reference's files only where all of them exist."""
+    sys.path.insert(0, ROOT) if ROOT not in sys.path else None
+    from oracle import build_ref
+    assert build_ref.build(str(tmp_path / "missing")) is False
+    (tmp_path / "empty").mkdir()
+    assert build_ref.build(str(tmp_path / "empty")) is False
